@@ -12,6 +12,10 @@ group (the reference has one implicit group: one block id spans all layers,
 kernels/batch_gpu.cu:75,114-118).  Groups with a window give pages back as soon as every later
 query is past them; their block tables then hold -1 at that place.
 
+An entry may also state a ``CompositeNeed``: several needs by name (pages AND a fixed-size state for one mixer;
+the needs of mixers that run side by side). Its leaves are placed as above, under the key (cache index, name, ...),
+and the entry's view is a dict of the same shape.
+
 Life of a request: ``admit`` (takes a state slot, zeroes its state) -> repeated ``reserve(n)``
 (pages for the next n positions in every group, all or nothing) + ``advance(n)`` (the positions
 are now filled; pages behind a window are freed) -> ``release`` (everything goes back).
@@ -23,7 +27,7 @@ from typing import Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts.base import PagedKVNeed, StateNeed
+from ..parts.base import CompositeNeed, PagedKVNeed, StateNeed
 
 
 class CacheError(RuntimeError):
@@ -84,7 +88,7 @@ class CacheGroup:
     pool: PagePool
     page_size: int
     k: Optional[torch.Tensor] = None     # [len(cache_ids), n_pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None     # the same with the need's value size last
 
     @property
     def window(self) -> Optional[int]:
@@ -120,22 +124,30 @@ class CacheManager:
         self.group_of_cache: Dict[int, Tuple[int, int]] = {}     # cache id -> (group index, index in group)
         self.state_needs: Dict[int, StateNeed] = {}
         self.state: Dict[int, Dict[str, torch.Tensor]] = {}
+        self.needs = dict(needs)
         by_key: Dict[Tuple, CacheGroup] = {}
-        for cid in sorted(needs):
-            need = needs[cid]
+
+        def place(key, need):
+            """key: the cache index, or (cache index, name, ...) for a leaf of a composite need."""
             if isinstance(need, PagedKVNeed):
-                key = (need.num_kv_heads, need.head_dim, need.window)
-                g = by_key.get(key)
+                gkey = (need.num_kv_heads, need.head_dim, need.value_dim, need.window)
+                g = by_key.get(gkey)
                 if g is None:
                     g = CacheGroup(len(self.groups), need, [], PagePool(n_pages), page_size)
-                    by_key[key] = g
+                    by_key[gkey] = g
                     self.groups.append(g)
-                self.group_of_cache[cid] = (g.index, len(g.cache_ids))
-                g.cache_ids.append(cid)
+                self.group_of_cache[key] = (g.index, len(g.cache_ids))
+                g.cache_ids.append(key)
             elif isinstance(need, StateNeed):
-                self.state_needs[cid] = need
+                self.state_needs[key] = need
+            elif isinstance(need, CompositeNeed):
+                for name, sub in need.parts.items():
+                    place((key if isinstance(key, tuple) else (key,)) + (name,), sub)
             elif need is not None:
-                raise TypeError(f"cache {cid}: unknown kind of need {need!r}")
+                raise TypeError(f"cache {key}: unknown kind of need {need!r}")
+
+        for cid in sorted(needs):
+            place(cid, needs[cid])
         self._free_slots = list(range(n_slots - 1, -1, -1))
         self.requests: Dict[Hashable, RequestCache] = {}
 
@@ -144,28 +156,35 @@ class CacheManager:
     def make_storage(self, dtype: torch.dtype, device) -> None:
         """Allocates the page tensors of every group and the state tensors of every state entry."""
         for g in self.groups:
-            shape = (len(g.cache_ids), g.pool.n_pages, g.need.num_kv_heads, self.page_size, g.need.head_dim)
-            g.k = torch.zeros(shape, dtype=dtype, device=device)
-            g.v = torch.zeros(shape, dtype=dtype, device=device)
+            shape = (len(g.cache_ids), g.pool.n_pages, g.need.num_kv_heads, self.page_size)
+            g.k = torch.zeros(shape + (g.need.head_dim,), dtype=dtype, device=device)
+            g.v = torch.zeros(shape + (g.need.value_dim,), dtype=dtype, device=device)
         for cid, need in self.state_needs.items():
-            self.state[cid] = {name: torch.zeros((self.n_slots,) + tuple(shape), dtype=dt, device=device)
+            # a state tensor declared with dtype None takes the storage's (the compute dtype of the model)
+            self.state[cid] = {name: torch.zeros((self.n_slots,) + tuple(shape), dtype=dt or dtype, device=device)
                                for name, (shape, dt) in need.shapes.items()}
 
     def storage_bytes(self, dtype: torch.dtype) -> int:
         item = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * len(g.cache_ids) * g.pool.n_pages * g.need.num_kv_heads * self.page_size * g.need.head_dim * item
-                   for g in self.groups)
+        return sum(len(g.cache_ids) * g.pool.n_pages * g.need.num_kv_heads * self.page_size *
+                   (g.need.head_dim + g.need.value_dim) * item for g in self.groups)
 
     def view(self, cache_id: int):
-        """PagedKVView, the dict of state tensors, or None for the given cache entry."""
-        if cache_id in self.group_of_cache:
-            gi, li = self.group_of_cache[cache_id]
+        """PagedKVView, the dict of state tensors, a dict of such views by name for a composite need, or None."""
+        return self._view(cache_id, self.needs.get(cache_id))
+
+    def _view(self, key, need):
+        if isinstance(need, CompositeNeed):
+            base = key if isinstance(key, tuple) else (key,)
+            return {name: self._view(base + (name,), sub) for name, sub in need.parts.items()}
+        if key in self.group_of_cache:
+            gi, li = self.group_of_cache[key]
             g = self.groups[gi]
             if g.k is None:
                 raise CacheError("make_storage() has not been called")
             return PagedKVView(gi, g.k[li], g.v[li], self.page_size, g.window)
-        if cache_id in self.state_needs:
-            return self.state[cache_id]
+        if key in self.state_needs:
+            return self.state[key]
         return None
 
     # ------------------------------------------------------------------ requests

@@ -1,4 +1,5 @@
-"""The one registry from an architecture's name (``config.json: architectures[0]``) to its model.
+"""The one registry from an architecture's name (``config.json: architectures[0]``, or its ``architecture`` string)
+to its model.
 
 An entry holds two callables: ``parse`` turns the raw config.json dictionary into the
 architecture's typed configuration, and ``to_spec`` turns that into the architecture-neutral
@@ -55,8 +56,10 @@ def registered_architectures():
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json needs a non-empty 'architectures' list of strings")
+        raise ConfigError("config.json needs a non-empty 'architectures' list of strings (or an 'architecture' string)")
     return get_architecture(archs[0])
 
 

@@ -32,7 +32,7 @@ class PartSpec:
 
 
 # The families a part can belong to; each has its own registry of kinds (``parts.base``).
-FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "gate")
 
 
 @dataclass(frozen=True)
@@ -89,6 +89,7 @@ class ModelSpec:
     embedding: PartSpec              # family "embedding": token ids -> float32 rows of the residual stream
     head: PartSpec                   # family "head": normalised rows -> float32 logits; may be tied to the embedding
     eos_token_id: Optional[int] = None
+    optional_tensors: Sequence[str] = ()   # names a checkpoint may hold although no part reads them
 
     def part_specs(self) -> Iterator[Tuple[str, PartSpec]]:
         """Every (family, PartSpec) of the model: embedding, head, final norm, then the layers' parts in order."""

@@ -29,6 +29,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 # module name -> source file; headers that every module depends on
 MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
+    "seq": "seq_ops.cu",         # filters over time, pair rotation, gated recurrence, side-by-side sublayers
     "gemvb": "gemv_bulk.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",

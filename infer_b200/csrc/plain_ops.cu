@@ -312,20 +312,21 @@ rope_kv_write_vec_kernel(const bf16* __restrict__ qkv, const float* __restrict__
 // The query at position p of its request reads keys lo..p, lo = max(0, p - window + 1) (window 0 =
 // all), from the pages of its request's block-table row. Keys are taken in tiles of 128 positions
 // aligned to absolute multiples of 128, softmax is computed online over the tiles, so the result
-// depends on (lo, p) only.
+// depends on (lo, p) only. Values may have another size than keys (v_dim; the value pages are
+// [kv_heads, page_size, v_dim] then), and the output rows are [heads, v_dim].
 constexpr int AT = 128;
 
 template <typename T>
 __global__ void __launch_bounds__(AT)
 attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                  const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
-                 const int* __restrict__ positions, T* __restrict__ out, int n_heads, int n_kv, int head_dim,
+                 const int* __restrict__ positions, T* __restrict__ out, int n_heads, int n_kv, int head_dim, int v_dim,
                  int page_size, int window, float scale, int64_t n_pages, int* status) {
     ib::pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                      // [head_dim]
     float* ps = qs + head_dim;             // [AT]
-    int64_t* rowoff = reinterpret_cast<int64_t*>(ps + AT);   // [AT] element offset of each key row
+    int64_t* rowoff = reinterpret_cast<int64_t*>(ps + AT);   // [AT] row of each key in the pages: (page, kv head, place)
     __shared__ float red[32];
 
     const int64_t t = blockIdx.x;
@@ -350,9 +351,9 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                 if (status) atomicExch(status, 3);
                 rowoff[tid] = 0;
             } else {
-                const int64_t off = ((int64_t(page) * n_kv + g) * page_size + j % page_size) * head_dim;
-                rowoff[tid] = off;
-                const T* kr = k_cache + off;
+                const int64_t row = (int64_t(page) * n_kv + g) * page_size + j % page_size;
+                rowoff[tid] = row;
+                const T* kr = k_cache + row * head_dim;
                 float dot = 0.0f;
                 for (int d = 0; d < head_dim; d++) dot = fmaf(qs[d], ib::to_f32(kr[d]), dot);
                 s = dot * scale;
@@ -370,17 +371,17 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
         const int jj0 = max(lo, tile) - tile, jj1 = min(pos, tile + AT - 1) - tile;
         for (int jj = jj0; jj <= jj1; jj++) {
             const float pj = ps[jj];
-            const T* vr = v_cache + rowoff[jj];
-            if (tid < head_dim) acc0 = fmaf(pj, ib::to_f32(vr[tid]), acc0);
-            if (tid + AT < head_dim) acc1 = fmaf(pj, ib::to_f32(vr[tid + AT]), acc1);
+            const T* vr = v_cache + rowoff[jj] * v_dim;
+            if (tid < v_dim) acc0 = fmaf(pj, ib::to_f32(vr[tid]), acc0);
+            if (tid + AT < v_dim) acc1 = fmaf(pj, ib::to_f32(vr[tid + AT]), acc1);
         }
         m = m_new;
         __syncthreads();
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    T* o = out + (t * n_heads + h) * head_dim;
-    if (tid < head_dim) o[tid] = ib::from_f32<T>(acc0 * inv);
-    if (tid + AT < head_dim) o[tid + AT] = ib::from_f32<T>(acc1 * inv);
+    T* o = out + (t * n_heads + h) * v_dim;
+    if (tid < v_dim) o[tid] = ib::from_f32<T>(acc0 * inv);
+    if (tid + AT < v_dim) o[tid + AT] = ib::from_f32<T>(acc1 * inv);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -690,20 +691,21 @@ IB_EXPORT int ib_attention_plain_max_head_dim() { return 2 * AT; }
 IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                  int64_t max_blocks, const int* token_seg, const int* positions, void* out,
                                  int64_t n_tokens, int n_heads, int n_kv, int head_dim, int page_size, int window,
-                                 float scale, int64_t n_pages, int dtype, int* status, cudaStream_t stream) {
+                                 float scale, int64_t n_pages, int dtype, int* status, cudaStream_t stream, int v_dim) {
     if (n_tokens <= 0) return IB_OK;
-    if (head_dim <= 0 || head_dim > 2 * AT)
-        return ib::fail(IB_ERR_ARG, "ib_attention_plain: head_dim %d is outside 1..%d", head_dim, 2 * AT);
+    if (v_dim <= 0) v_dim = head_dim;                       // values as long as keys
+    if (head_dim <= 0 || head_dim > 2 * AT || v_dim > 2 * AT)
+        return ib::fail(IB_ERR_ARG, "ib_attention_plain: head sizes %d / %d are outside 1..%d", head_dim, v_dim, 2 * AT);
     if (n_kv <= 0 || n_heads % n_kv) return ib::fail(IB_ERR_ARG, "ib_attention_plain: heads %d not a multiple of kv heads %d", n_heads, n_kv);
     if (n_heads > 65535) return ib::fail(IB_ERR_ARG, "ib_attention_plain: too many heads");
     const dim3 grid{unsigned(n_tokens), unsigned(n_heads), 1u};
     const size_t smem = size_t(head_dim + AT) * sizeof(float) + AT * sizeof(int64_t) + 8;
     if (dtype == IB_F32)
         IB_LAUNCH(attention_kernel<float>, grid, AT, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache,
-            block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, page_size, window, scale, n_pages, status);
+            block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status);
     else if (dtype == IB_BF16)
         IB_LAUNCH(attention_kernel<bf16>, grid, AT, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-            block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, page_size, window, scale, n_pages, status);
+            block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status);
     else
         return ib::fail(IB_ERR_ARG, "ib_attention_plain: unknown dtype %d", dtype);
     return ib::check_launch("ib_attention_plain");

@@ -1,0 +1,448 @@
+// Kernels for layers that carry more per request than pages of keys and values: short causal filters over time with
+// their tails, rotation of adjacent pairs over part of a head, values normalised before they are cached, a gated
+// linear recurrence with a matrix state per head, and the element-wise pieces of a layer whose sublayers run side
+// by side (tanh-GELU, per-head output gates, the gated residual sum).
+//
+// Storage is float or bfloat16 (template parameter), arithmetic float. Recurrent state, gates of the recurrence,
+// norms, angles and the residual sum are float in both. With float storage these kernels are the 32-bit path.
+//
+// Every kernel takes a step's packed rows: tokens of several requests ("segments") one after the other, seg_start[s]
+// the first row of segment s, seg_slot[s] the request's state slot. What a token's result depends on is its own
+// request's earlier tokens and state only, and every reduction runs in an order fixed by the layer's sizes, so a
+// result does not depend on how a prompt was cut or on what else is in the step.
+#include "common.cuh"
+
+IB_DEFINE_LAST_ERROR()
+
+#define IB_LAUNCH(kernel, grid, block, smem, ...)                                                              \
+    do {                                                                                                       \
+        const int rc_ = ib::launch(#kernel, kernel, dim3(grid), dim3(block), size_t(smem), stream, 1u, __VA_ARGS__); \
+        if (rc_) return rc_;                                                                                   \
+    } while (0)
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + threads - 1) / threads); }
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------
+// Short causal filter, per channel: y[t] = sum_j w[c, j] * u[t - (taps - 1) + j]. u before the first row of the
+// step's segment comes from the request's tail (the last taps - 1 values of earlier steps, oldest first; zeros for a
+// new request, which is what "nothing before the start" means). i_local is the token's index within its segment;
+// `col` its channel's column in the rows, `tail` the channel's first tail value, tail_ld the channel count.
+template <typename T>
+__device__ __forceinline__ float filtered(const T* __restrict__ rows, int64_t ld, int64_t t, int i_local, int col,
+                                          const float* __restrict__ w, int taps, const T* __restrict__ tail,
+                                          int64_t tail_ld) {
+    if (taps <= 1) {
+        const float u = ib::to_f32(rows[t * ld + col]);
+        return taps == 1 ? w[0] * u : u;
+    }
+    float y = 0.0f;
+    for (int j = 0; j < taps; j++) {
+        const int back = taps - 1 - j;
+        const float u = i_local >= back ? ib::to_f32(rows[(t - back) * ld + col])
+                                        : ib::to_f32(tail[int64_t(taps - 1 + i_local - back) * tail_ld]);
+        y = fmaf(w[j], u, y);
+    }
+    return y;
+}
+
+template <typename T>
+__global__ void short_filter_kernel(const T* __restrict__ rows, int64_t ld, int col0, int channels,
+                                    const float* __restrict__ w, int taps, const T* __restrict__ tails,
+                                    const int* __restrict__ token_seg, const int* __restrict__ seg_start,
+                                    const int* __restrict__ seg_slot, T* __restrict__ out, int64_t n_tokens) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * channels) return;
+    const int64_t t = i / channels;
+    const int c = int(i - t * channels);
+    const int s = token_seg[t];
+    const T* tail = tails ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c : nullptr;
+    out[i] = ib::from_f32<T>(filtered(rows, ld, t, int(t - seg_start[s]), col0 + c, w + int64_t(c) * taps, taps, tail, channels));
+}
+
+// After a step: the tail of every segment's request becomes the last taps - 1 values of (old tail, the step's rows).
+// One thread per (segment, channel) moves its values oldest first, reading ahead of what it writes.
+template <typename T>
+__global__ void filter_tail_kernel(const T* __restrict__ rows, int64_t ld, int col0, int channels, int taps,
+                                   T* __restrict__ tails, const int* __restrict__ seg_start,
+                                   const int* __restrict__ seg_slot) {
+    ib::pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = blockIdx.y;
+    if (c >= channels) return;
+    const int keep = taps - 1;
+    const int64_t t0 = seg_start[s];
+    const int len = int(seg_start[s + 1] - t0);
+    T* tail = tails + (int64_t(seg_slot[s]) * keep) * channels + c;
+    for (int idx = 0; idx < keep; idx++) {
+        const int src = len - keep + idx;
+        tail[int64_t(idx) * channels] = src >= 0 ? rows[(t0 + src) * ld + col0 + c] : tail[int64_t(idx + len) * channels];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// From projected rows [q heads | k heads | v heads | ...] to what attention reads: optional short filter on every
+// channel, rotation of q and k, optional normalisation of v, q into q_out, k and v into the token's page.
+// Rotation: channels (2i, 2i + 1) of a head, 2i < n_rot, turn by the angle of tables cos/sin [positions, n_rot / 2];
+// the head's other channels stay.  v: each head divided by sqrt(mean(v^2) + eps), no weight.
+// One warp per (token, head of q, k or v); a lane keeps up to PREP_PAIRS pairs of a head in registers.
+constexpr int PREP_PAIRS = 4;           // heads of up to 64 * PREP_PAIRS channels
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, const float* __restrict__ filt_w, int taps,
+                   const T* __restrict__ tails, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                   int n_rot, int norm_v, float eps, const int* __restrict__ positions,
+                   const int* __restrict__ token_seg, const int* __restrict__ seg_start,
+                   const int* __restrict__ seg_slot, const int* __restrict__ block_table, int64_t max_blocks,
+                   T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, int64_t n_tokens,
+                   int n_heads, int n_kv, int d, int dv, int page_size, int write_cache, int64_t n_pages, int* status) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int units = n_heads + 2 * n_kv;
+    const int64_t wi = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wi >= n_tokens * units) return;
+    const int64_t t = wi / units;
+    const int u = int(wi - t * units);
+    const int kind = u < n_heads ? 0 : (u < n_heads + n_kv ? 1 : 2);            // q, k, v
+    const int head = kind == 0 ? u : (kind == 1 ? u - n_heads : u - n_heads - n_kv);
+    const int width = kind == 2 ? dv : d;
+    const int col0 = kind == 0 ? head * d : (kind == 1 ? n_heads * d + head * d : (n_heads + n_kv) * d + head * dv);
+    const int channels = (n_heads + n_kv) * d + n_kv * dv;
+    const int s = token_seg[t];
+    const int i_local = int(t - seg_start[s]);
+    const int pos = positions[t];
+    const bool filt = filt_w != nullptr && taps > 0;
+    const T* tail = filt && taps > 1 ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels : nullptr;
+
+    float a[PREP_PAIRS], b[PREP_PAIRS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int r = 0; r < PREP_PAIRS; r++) {
+        const int p = lane + 32 * r;
+        a[r] = b[r] = 0.0f;
+        if (2 * p < width) {
+            const int c = col0 + 2 * p;
+            if (filt) {
+                a[r] = filtered(rows, ld, t, i_local, c, filt_w + int64_t(c) * taps, taps, tail + c, channels);
+                b[r] = filtered(rows, ld, t, i_local, c + 1, filt_w + int64_t(c + 1) * taps, taps, tail + c + 1, channels);
+            } else {
+                a[r] = ib::to_f32(rows[t * ld + c]);
+                b[r] = ib::to_f32(rows[t * ld + c + 1]);
+            }
+            if (kind != 2 && cos_t && 2 * p < n_rot) {
+                const float cs = cos_t[int64_t(pos) * (n_rot / 2) + p], sn = sin_t[int64_t(pos) * (n_rot / 2) + p];
+                const float ra = a[r] * cs - b[r] * sn;
+                const float rb = b[r] * cs + a[r] * sn;
+                a[r] = ra;
+                b[r] = rb;
+            }
+            ss = fmaf(a[r], a[r], ss);
+            ss = fmaf(b[r], b[r], ss);
+        }
+    }
+    if (kind == 2 && norm_v) {
+        ss = ib::warp_sum(ss);
+        const float f = rsqrtf(ss / float(width) + eps);
+#pragma unroll
+        for (int r = 0; r < PREP_PAIRS; r++) {
+            a[r] *= f;
+            b[r] *= f;
+        }
+    }
+    T* dst;
+    if (kind == 0) {
+        dst = q_out + (t * n_heads + head) * d;
+    } else {
+        if (!write_cache) return;
+        const int page = block_table[int64_t(s) * max_blocks + pos / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (status && lane == 0) atomicExch(status, 2);
+            return;
+        }
+        dst = (kind == 1 ? k_cache : v_cache) + ((int64_t(page) * n_kv + head) * page_size + pos % page_size) * width;
+    }
+#pragma unroll
+    for (int r = 0; r < PREP_PAIRS; r++) {
+        const int p = lane + 32 * r;
+        if (2 * p < width) {
+            dst[2 * p] = ib::from_f32<T>(a[r]);
+            dst[2 * p + 1] = ib::from_f32<T>(b[r]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// ctx[t, h, :] *= sigmoid(gate[t, h]); the gate logits are columns gate_col .. gate_col + heads of the rows.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ ctx, const T* __restrict__ rows, int64_t ld, int gate_col,
+                                 int64_t n_tokens, int n_heads, int dv) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * n_heads * dv) return;
+    const int64_t th = i / dv;
+    const int64_t t = th / n_heads;
+    const int h = int(th - t * n_heads);
+    const float g = sigmoidf_(ib::to_f32(rows[t * ld + gate_col + h]));
+    ctx[i] = ib::from_f32<T>(ib::to_f32(ctx[i]) * g);
+}
+
+// ------------------------------------------------------------------------------------------------
+// tanh-GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float z = ib::to_f32(x[i]);
+    out[i] = ib::from_f32<T>(0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+}
+
+// ------------------------------------------------------------------------------------------------
+// out = x + sigmoid(g1) * (a * p + b * q) + sigmoid(g2) * r, all float [tokens, width]; the gate logits are columns
+// [0, width) and [width, 2 width) of rows `gates` with leading dimension ldg. q, r (and then g2) may be absent; with
+// gates absent the terms are added as they are.
+__global__ void gated_sum_kernel(const float* x, const float* __restrict__ gates, int64_t ldg,
+                                 const float* __restrict__ p, float a, const float* __restrict__ q, float b,
+                                 const float* __restrict__ r, float* out, int64_t n_tokens, int64_t width) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * width) return;
+    const int64_t t = i / width, c = i - t * width;
+    float m = a * p[i];
+    if (q) m = fmaf(b, q[i], m);
+    float y = gates ? sigmoidf_(gates[t * ldg + c]) * m : m;
+    if (r) y += gates ? sigmoidf_(gates[t * ldg + width + c]) * r[i] : r[i];
+    out[i] = x[i] + y;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Gated linear recurrence with a matrix state per head (the forget gate also weighs what is written):
+//   f = low + (1 - low) * sigmoid(f_raw),  q = silu(q_raw)
+//   S <- diag(f) S + (1 - f) v^T          S [d, dv] float, per request and head, kept in `state` between steps
+//   o = S^T q,  out = o / sqrt(mean(o^2) + eps) * norm_w      (per head; norm_w [dv] shared by the heads)
+// Rows `proj` are float [tokens, ld] with q_raw at q_col, f_raw at f_col (both heads * d wide) and v at v_col
+// (heads * dv wide).  One CTA per (segment, head) walks over the segment's tokens in order.  Thread (kg, col) keeps
+// rows kg * kpt .. of column col of S in registers; tokens are staged `chunk` at a time in shared memory, the
+// column sums over kg are added in ascending order.
+constexpr int REC_MAXK = 32, REC_THREADS = 512;
+
+template <typename TOut>
+__global__ void __launch_bounds__(REC_THREADS)
+gated_recurrence_kernel(const float* __restrict__ proj, int64_t ld, int q_col, int f_col, int v_col,
+                        const float* __restrict__ lower, const float* __restrict__ norm_w, float eps,
+                        float* __restrict__ state, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                        TOut* __restrict__ out, int n_heads, int d, int dv, int ks, int kpt, int chunk, int write_state) {
+    ib::pdl_wait();
+    extern __shared__ float sm[];
+    float* qs = sm;                          // [chunk][d]
+    float* fs = qs + chunk * d;              // [chunk][d]
+    float* vs = fs + chunk * d;              // [chunk][dv]
+    float* part = vs + chunk * dv;           // [chunk][ks][dv]
+    float* os = part + chunk * ks * dv;      // [chunk][dv]
+    const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    const int col = tid % dv, kg = tid / dv;
+    const int k0 = kg * kpt;
+    const int nk = kg < ks ? max(0, min(kpt, d - k0)) : 0;
+    const int64_t t0 = seg_start[s];
+    const int len = int(seg_start[s + 1] - t0);
+    float* S_g = state + (int64_t(seg_slot[s]) * n_heads + h) * int64_t(d) * dv;
+    float S[REC_MAXK];
+#pragma unroll
+    for (int kk = 0; kk < REC_MAXK; kk++) S[kk] = kk < nk ? S_g[int64_t(k0 + kk) * dv + col] : 0.0f;
+
+    for (int c0 = 0; c0 < len; c0 += chunk) {
+        const int n = min(chunk, len - c0);
+        for (int idx = tid; idx < n * d; idx += blockDim.x) {
+            const int c = idx / d, k = idx - c * d;
+            const float* row = proj + (t0 + c0 + c) * ld;
+            const float qr = row[q_col + h * d + k];
+            qs[idx] = qr / (1.0f + expf(-qr));
+            const float lo = lower[h * d + k];
+            fs[idx] = lo + (1.0f - lo) * sigmoidf_(row[f_col + h * d + k]);
+        }
+        for (int idx = tid; idx < n * dv; idx += blockDim.x) {
+            const int c = idx / dv, j = idx - c * dv;
+            vs[idx] = proj[(t0 + c0 + c) * ld + v_col + h * dv + j];
+        }
+        __syncthreads();
+        if (kg < ks) {
+            for (int c = 0; c < n; c++) {
+                const float v = vs[c * dv + col];
+                const float* fr = fs + c * d + k0;
+                const float* qr = qs + c * d + k0;
+                float acc = 0.0f;
+#pragma unroll
+                for (int kk = 0; kk < REC_MAXK; kk++) {
+                    if (kk < nk) {
+                        const float f = fr[kk];
+                        S[kk] = fmaf(f, S[kk], (1.0f - f) * v);
+                        acc = fmaf(S[kk], qr[kk], acc);
+                    }
+                }
+                part[(c * ks + kg) * dv + col] = acc;
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < n * dv; idx += blockDim.x) {
+            const int c = idx / dv, j = idx - c * dv;
+            float o = 0.0f;
+            for (int g = 0; g < ks; g++) o += part[(c * ks + g) * dv + j];
+            os[idx] = o;
+        }
+        __syncthreads();
+        for (int c = warp; c < n; c += n_warps) {
+            float ss = 0.0f;
+            for (int j = lane; j < dv; j += 32) ss = fmaf(os[c * dv + j], os[c * dv + j], ss);
+            ss = ib::warp_sum(ss);
+            const float f = rsqrtf(ss / float(dv) + eps);
+            TOut* o = out + ((t0 + c0 + c) * n_heads + h) * int64_t(dv);
+            for (int j = lane; j < dv; j += 32) o[j] = ib::from_f32<TOut>(os[c * dv + j] * f * norm_w[j]);
+        }
+        __syncthreads();
+    }
+    if (write_state) {
+#pragma unroll
+        for (int kk = 0; kk < REC_MAXK; kk++)
+            if (kk < nk) S_g[int64_t(k0 + kk) * dv + col] = S[kk];
+    }
+}
+
+}  // namespace
+
+// ================================================================================================
+// C entry points. dtype arguments: 0 = float, 1 = bfloat16.
+
+IB_EXPORT int ib_short_filter(const void* rows, int64_t ld, int col0, int channels, const float* w, int taps,
+                              const void* tails, const int* token_seg, const int* seg_start, const int* seg_slot,
+                              void* out, int64_t n_tokens, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || channels <= 0) return IB_OK;
+    if (taps < 1 || (taps > 1 && !tails)) return ib::fail(IB_ERR_ARG, "ib_short_filter: taps %d, or no tails", taps);
+    const int64_t n = n_tokens * channels;
+    if (dtype == IB_F32)
+        IB_LAUNCH(short_filter_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)rows, ld, col0, channels, w, taps,
+                  (const float*)tails, token_seg, seg_start, seg_slot, (float*)out, n_tokens);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(short_filter_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)rows, ld, col0, channels, w, taps,
+                  (const bf16*)tails, token_seg, seg_start, seg_slot, (bf16*)out, n_tokens);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_short_filter: unknown dtype %d", dtype);
+    return ib::check_launch("ib_short_filter");
+}
+
+IB_EXPORT int ib_filter_tail(const void* rows, int64_t ld, int col0, int channels, int taps, void* tails,
+                             const int* seg_start, const int* seg_slot, int n_segments, int dtype, cudaStream_t stream) {
+    if (n_segments <= 0 || channels <= 0 || taps <= 1) return IB_OK;
+    if (n_segments > 65535) return ib::fail(IB_ERR_ARG, "ib_filter_tail: too many segments");
+    const dim3 grid{blocks_for(channels, 128), unsigned(n_segments), 1u};
+    if (dtype == IB_F32)
+        IB_LAUNCH(filter_tail_kernel<float>, grid, 128, 0, (const float*)rows, ld, col0, channels, taps, (float*)tails, seg_start, seg_slot);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(filter_tail_kernel<bf16>, grid, 128, 0, (const bf16*)rows, ld, col0, channels, taps, (bf16*)tails, seg_start, seg_slot);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_filter_tail: unknown dtype %d", dtype);
+    return ib::check_launch("ib_filter_tail");
+}
+
+// The widest head (keys or values) that ib_qkv_prepare takes.
+IB_EXPORT int ib_qkv_prepare_max_head_dim() { return 64 * PREP_PAIRS; }
+
+IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, const float* filt_w, int taps, const void* tails,
+                             const float* cos_t, const float* sin_t, int n_rot, int norm_v, float eps,
+                             const int* positions, const int* token_seg, const int* seg_start, const int* seg_slot,
+                             const int* block_table, int64_t max_blocks, void* q_out, void* k_cache, void* v_cache,
+                             int64_t n_tokens, int n_heads, int n_kv, int d, int dv, int page_size, int write_cache,
+                             int64_t n_pages, int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (d <= 0 || dv <= 0 || d % 2 || dv % 2 || d > 64 * PREP_PAIRS || dv > 64 * PREP_PAIRS)
+        return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: head sizes %d / %d must be even and at most %d", d, dv, 64 * PREP_PAIRS);
+    if (n_rot < 0 || n_rot % 2 || n_rot > d) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: %d rotated channels of %d", n_rot, d);
+    if (filt_w && taps > 1 && !tails) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: a filter of %d taps needs tails", taps);
+    if (n_heads <= 0 || n_kv <= 0 || page_size <= 0) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: bad sizes");
+    const int64_t warps = n_tokens * (n_heads + 2 * n_kv);
+    if (dtype == IB_F32)
+        IB_LAUNCH(qkv_prepare_kernel<float>, blocks_for(warps, 4), 128, 0, (const float*)rows, ld, filt_w, taps, (const float*)tails, cos_t, sin_t,
+                  n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (float*)q_out,
+                  (float*)k_cache, (float*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(qkv_prepare_kernel<bf16>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, filt_w, taps, (const bf16*)tails, cos_t, sin_t,
+                  n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
+                  (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: unknown dtype %d", dtype);
+    return ib::check_launch("ib_qkv_prepare");
+}
+
+IB_EXPORT int ib_head_gate(void* ctx, const void* rows, int64_t ld, int gate_col, int64_t n_tokens, int n_heads, int dv,
+                           int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    const int64_t n = n_tokens * n_heads * dv;
+    if (dtype == IB_F32)
+        IB_LAUNCH(head_gate_kernel<float>, blocks_for(n, 256), 256, 0, (float*)ctx, (const float*)rows, ld, gate_col, n_tokens, n_heads, dv);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(head_gate_kernel<bf16>, blocks_for(n, 256), 256, 0, (bf16*)ctx, (const bf16*)rows, ld, gate_col, n_tokens, n_heads, dv);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_head_gate: unknown dtype %d", dtype);
+    return ib::check_launch("ib_head_gate");
+}
+
+IB_EXPORT int ib_gelu_tanh(const void* x, void* out, int64_t n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return IB_OK;
+    if (dtype == IB_F32)
+        IB_LAUNCH(gelu_tanh_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)x, (float*)out, n);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(gelu_tanh_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)x, (bf16*)out, n);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_gelu_tanh: unknown dtype %d", dtype);
+    return ib::check_launch("ib_gelu_tanh");
+}
+
+IB_EXPORT int ib_gated_sum(const float* x, const float* gates, int64_t ldg, const float* p, float a, const float* q,
+                           float b, const float* r, float* out, int64_t n_tokens, int64_t width, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0) return IB_OK;
+    if (!p) return ib::fail(IB_ERR_ARG, "ib_gated_sum: the first term is missing");
+    IB_LAUNCH(gated_sum_kernel, blocks_for(n_tokens * width, 256), 256, 0, x, gates, ldg, p, a, q, b, r, out, n_tokens, width);
+    return ib::check_launch("ib_gated_sum");
+}
+
+// The largest d * dv of a head's state that ib_gated_recurrence takes (threads of a CTA x rows a thread keeps).
+IB_EXPORT int64_t ib_gated_recurrence_max_state() { return int64_t(REC_THREADS) * REC_MAXK; }
+
+IB_EXPORT int ib_gated_recurrence(const float* proj, int64_t ld, int q_col, int f_col, int v_col, const float* lower,
+                                  const float* norm_w, float eps, float* state, const int* seg_start,
+                                  const int* seg_slot, void* out, int n_segments, int n_heads, int d, int dv,
+                                  int write_state, int out_dtype, cudaStream_t stream) {
+    if (n_segments <= 0) return IB_OK;
+    if (d <= 0 || dv <= 0 || n_heads <= 0 || dv > REC_THREADS) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: bad sizes %d x %d", d, dv);
+    if (n_heads > 65535) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: too many heads");
+    // rows of the state are shared among `ks` threads per column: as few as keep a thread's share within REC_MAXK
+    // rows, but enough to fill a CTA of 256 threads where the head allows. The choice depends on (d, dv) only.
+    int ks = (d + REC_MAXK - 1) / REC_MAXK;
+    while (ks * dv < 256 && ks < d && (ks + 1) * dv <= REC_THREADS) ks++;
+    if (int64_t(ks) * dv > REC_THREADS)
+        return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: a head's state of %d x %d is beyond %d rows x %d threads", d, dv, REC_MAXK, REC_THREADS);
+    const int kpt = (d + ks - 1) / ks;
+    const int threads = (ks * dv + 31) / 32 * 32;
+    const int per_token = 2 * d + dv + ks * dv + dv;
+    int chunk = 11264 / per_token;                           // 44 KB of staging at most
+    chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
+    const size_t smem = size_t(chunk) * per_token * sizeof(float);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: a token of %d floats does not fit the staging area", per_token);
+    const dim3 grid{unsigned(n_segments), unsigned(n_heads), 1u};
+    if (out_dtype == IB_F32)
+        IB_LAUNCH(gated_recurrence_kernel<float>, grid, threads, smem, proj, ld, q_col, f_col, v_col, lower, norm_w, eps, state,
+                  seg_start, seg_slot, (float*)out, n_heads, d, dv, ks, kpt, chunk, write_state);
+    else if (out_dtype == IB_BF16)
+        IB_LAUNCH(gated_recurrence_kernel<bf16>, grid, threads, smem, proj, ld, q_col, f_col, v_col, lower, norm_w, eps, state,
+                  seg_start, seg_slot, (bf16*)out, n_heads, d, dv, ks, kpt, chunk, write_state);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: unknown output dtype %d", out_dtype);
+    return ib::check_launch("ib_gated_recurrence");
+}

@@ -186,25 +186,28 @@ def rope_kv_write(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[
 
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                     token_seg: torch.Tensor, positions: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
-                    window: Optional[int], scale: float, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal attention of every token over its request's pages; returns [T, heads*head_dim]."""
+                    window: Optional[int], scale: float, status: Optional[torch.Tensor] = None,
+                    v_head_dim: Optional[int] = None) -> torch.Tensor:
+    """Causal attention of every token over its request's pages; returns [T, heads*v_head_dim] (values are as long
+    as keys unless ``v_head_dim`` says otherwise; the value pages are [pages, kv_heads, page_size, v_head_dim])."""
     _check(q, "q")
     T = q.shape[0]
+    vd = int(v_head_dim or head_dim)
     _check(q, "q", None, (T, n_heads * head_dim))
     _check(k_cache, "k_cache", q.dtype)
-    _check(v_cache, "v_cache", q.dtype, k_cache.shape)
     n_pages, ckv, page_size, chd = k_cache.shape
+    _check(v_cache, "v_cache", q.dtype, (n_pages, ckv, page_size, vd))
     if ckv != n_kv or chd != head_dim:
         raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match kv_heads={n_kv}, head_dim={head_dim}")
     _check(positions, "positions", torch.int32, (T,))
     _check(token_seg, "token_seg", torch.int32, (T,))
     _check(block_table, "block_table", torch.int32)
-    out = torch.empty_like(q)
+    out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
     f = _fn("plain", "ib_attention_plain", [c_void_p] * 4 + [c_int64] + [c_void_p] * 3 + [c_int64] + [c_int] * 5 +
-            [c_float, c_int64, c_int, c_void_p, c_void_p])
+            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int])
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           token_seg.data_ptr(), positions.data_ptr(), out.data_ptr(), T, n_heads, n_kv, head_dim, page_size,
-          int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream())
+          int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream(), vd)
     return out
 
 
@@ -258,4 +261,165 @@ def sample_filtered(logits: torch.Tensor, temperature: torch.Tensor, seed: torch
     f = _fn("plain", "ib_sample_filtered", [c_void_p, c_int64, c_int64] + [c_void_p] * 9)
     _call(f, logits.data_ptr(), B, V, temperature.data_ptr(), seed.data_ptr(), step.data_ptr(), top_k.data_ptr(),
           top_p.data_ptr(), out.data_ptr(), _ptr(feedback), _ptr(slots), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- kernels of layers with state
+
+def short_filter(rows: torch.Tensor, col0: int, weight: torch.Tensor, tails: Optional[torch.Tensor],
+                 token_seg: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor) -> torch.Tensor:
+    """Causal filter over time on columns [col0, col0 + C) of ``rows`` [T, ld]: y[t, c] = sum_j weight[c, j] *
+    u[t - (taps - 1) + j, c], where u before a segment's first row comes from ``tails`` [slots, taps - 1, C]
+    (oldest first). weight float32 [C, taps]. Returns [T, C] in the rows' dtype; the tails are not changed."""
+    _check(rows, "rows")
+    T, ld = rows.shape
+    _check(weight, "weight", torch.float32)
+    C, taps = weight.shape
+    if tails is not None:
+        _check(tails, "tails", rows.dtype)
+        if tuple(tails.shape[1:]) != (taps - 1, C):
+            raise KernelError(f"tails must be [slots, {taps - 1}, {C}], got {tuple(tails.shape)}")
+    _check(token_seg, "token_seg", torch.int32, (T,))
+    out = torch.empty((T, C), dtype=rows.dtype, device=rows.device)
+    f = _fn("seq", "ib_short_filter", [c_void_p, c_int64, c_int, c_int, c_void_p, c_int] + [c_void_p] * 5 + [c_int64, c_int, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(col0), C, weight.data_ptr(), taps, _ptr(tails), token_seg.data_ptr(),
+          seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), T, dtype_code(rows.dtype), _stream())
+    return out
+
+
+def filter_tail_update(rows: torch.Tensor, col0: int, tails: torch.Tensor, seg_start: torch.Tensor,
+                       seg_slot: torch.Tensor) -> None:
+    """After a step: tails[slot of s] becomes the last taps - 1 values of (old tail, the rows of segment s)."""
+    _check(rows, "rows")
+    _check(tails, "tails", rows.dtype)
+    keep, C = tails.shape[1], tails.shape[2]
+    S = seg_slot.numel()
+    f = _fn("seq", "ib_filter_tail", [c_void_p, c_int64, c_int, c_int, c_int] + [c_void_p] * 3 + [c_int, c_int, c_void_p])
+    _call(f, rows.data_ptr(), rows.shape[1], int(col0), C, keep + 1, tails.data_ptr(), seg_start.data_ptr(),
+          seg_slot.data_ptr(), S, dtype_code(rows.dtype), _stream())
+
+
+def qkv_prepare_max_head_dim() -> int:
+    return int(_fn("seq", "ib_qkv_prepare_max_head_dim", [])())
+
+
+def qkv_prepare(rows: torch.Tensor, filt_w: Optional[torch.Tensor], tails: Optional[torch.Tensor],
+                cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], n_rot: int, norm_v: bool, eps: float,
+                step, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, write_cache: bool = True) -> torch.Tensor:
+    """Projected rows [q | k | v | anything] -> q [T, heads * head_dim] for attention, k and v into their pages.
+    Optional on the way: a short causal filter on every q, k and v channel (``filt_w`` float32 [channels, taps] with
+    the requests' ``tails`` [slots, taps - 1, channels]); rotation of adjacent channel pairs of q and k over the
+    first ``n_rot`` channels of each head (tables float32 [positions, n_rot / 2]); v divided by its root mean square
+    per head (``norm_v``). ``step`` gives positions, token_seg, seg_start, seg_slot and the status word."""
+    _check(rows, "rows")
+    T, ld = rows.shape
+    C = (n_heads + n_kv) * head_dim + n_kv * v_head_dim
+    if ld < C:
+        raise KernelError(f"rows of {ld} columns cannot hold q, k and v of {C}")
+    n_pages, ckv, page_size, chd = k_cache.shape
+    _check(k_cache, "k_cache", rows.dtype, (n_pages, n_kv, page_size, head_dim))
+    _check(v_cache, "v_cache", rows.dtype, (n_pages, n_kv, page_size, v_head_dim))
+    taps = 0
+    if filt_w is not None:
+        _check(filt_w, "filt_w", torch.float32)
+        if filt_w.shape[0] != C:
+            raise KernelError(f"the filter has {filt_w.shape[0]} channels, the rows {C}")
+        taps = filt_w.shape[1]
+        if taps > 1:
+            _check(tails, "tails", rows.dtype)
+            if tuple(tails.shape[1:]) != (taps - 1, C):
+                raise KernelError(f"tails must be [slots, {taps - 1}, {C}], got {tuple(tails.shape)}")
+    if cos is not None:
+        _check(cos, "cos", torch.float32)
+        _check(sin, "sin", torch.float32, cos.shape)
+        if cos.shape[1] != n_rot // 2:
+            raise KernelError("rotation tables must be [positions, n_rot / 2]")
+    else:
+        n_rot = 0
+    _check(block_table, "block_table", torch.int32)
+    q = torch.empty((T, n_heads * head_dim), dtype=rows.dtype, device=rows.device)
+    f = _fn("seq", "ib_qkv_prepare", [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float] +
+            [c_void_p] * 5 + [c_int64] + [c_void_p] * 3 + [c_int64] + [c_int] * 6 + [c_int64, c_int, c_void_p, c_void_p])
+    _call(f, rows.data_ptr(), ld, _ptr(filt_w), taps, _ptr(tails) if taps > 1 else None, _ptr(cos), _ptr(sin),
+          int(n_rot), int(bool(norm_v)), float(eps), step.positions.data_ptr(), step.token_seg.data_ptr(),
+          step.seg_start.data_ptr(), step.seg_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+          q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T, n_heads, n_kv, head_dim, v_head_dim, page_size,
+          int(write_cache), n_pages, dtype_code(rows.dtype), _ptr(step.status), _stream())
+    return q
+
+
+def head_gate(ctx: torch.Tensor, rows: torch.Tensor, gate_col: int, n_heads: int, v_head_dim: int) -> torch.Tensor:
+    """In place: ctx[t, h, :] *= sigmoid(rows[t, gate_col + h])."""
+    _check(ctx, "ctx")
+    T = ctx.shape[0]
+    _check(ctx, "ctx", None, (T, n_heads * v_head_dim))
+    _check(rows, "rows", ctx.dtype)
+    if rows.shape[0] != T or rows.shape[1] < gate_col + n_heads:
+        raise KernelError("the gate columns lie outside the rows")
+    f = _fn("seq", "ib_head_gate", [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_int, c_void_p])
+    _call(f, ctx.data_ptr(), rows.data_ptr(), rows.shape[1], int(gate_col), T, n_heads, v_head_dim, dtype_code(ctx.dtype), _stream())
+    return ctx
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    """0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), element by element."""
+    _check(x, "x")
+    out = torch.empty_like(x)
+    f = _fn("seq", "ib_gelu_tanh", [c_void_p, c_void_p, c_int64, c_int, c_void_p])
+    _call(f, x.data_ptr(), out.data_ptr(), x.numel(), dtype_code(x.dtype), _stream())
+    return out
+
+
+def gated_sum(x: torch.Tensor, gates: Optional[torch.Tensor], p: torch.Tensor, a: float = 1.0,
+              q: Optional[torch.Tensor] = None, b: float = 1.0, r: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x + sigmoid(gates[:, :W]) * (a p + b q) + sigmoid(gates[:, W:2W]) * r, float32 [T, W], written over x.
+    q and r may be absent; without gates the terms are added as they are."""
+    _check(x, "x", torch.float32)
+    T, W = x.shape
+    for name, t in (("p", p), ("q", q), ("r", r)):
+        if t is not None:
+            _check(t, name, torch.float32, (T, W))
+    ldg = 0
+    if gates is not None:
+        _check(gates, "gates", torch.float32)
+        ldg = gates.shape[1]
+        if gates.shape[0] != T or ldg < (2 * W if r is not None else W):
+            raise KernelError(f"gates of shape {tuple(gates.shape)} do not cover the terms")
+    f = _fn("seq", "ib_gated_sum", [c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p,
+                                    c_int64, c_int64, c_void_p])
+    _call(f, x.data_ptr(), _ptr(gates), ldg, p.data_ptr(), float(a), _ptr(q), float(b), _ptr(r), x.data_ptr(), T, W, _stream())
+    return x
+
+
+def gated_recurrence_max_state() -> int:
+    f = _fn("seq", "ib_gated_recurrence_max_state", [], restype=c_int64)
+    return int(f())
+
+
+def gated_recurrence(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, lower: torch.Tensor,
+                     norm_weight: torch.Tensor, eps: float, state: torch.Tensor, seg_start: torch.Tensor,
+                     seg_slot: torch.Tensor, n_heads: int, dim: int, v_dim: int, out_dtype: torch.dtype,
+                     write_state: bool = True) -> torch.Tensor:
+    """The gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q per head, over the tokens of every
+    segment in order, from and into ``state`` float32 [slots, heads, dim, v_dim]; f = lower + (1 - lower) *
+    sigmoid(proj[:, f_col:]), q = silu(proj[:, q_col:]), v = proj[:, v_col:] (proj float32 [T, ld]). Each head's o is
+    divided by its root mean square and multiplied by ``norm_weight`` [v_dim]. Returns [T, heads * v_dim]."""
+    _check(proj, "proj", torch.float32)
+    T, ld = proj.shape
+    _check(lower, "lower", torch.float32, (n_heads * dim,))
+    _check(norm_weight, "norm_weight", torch.float32, (v_dim,))
+    _check(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (n_heads, dim, v_dim):
+        raise KernelError(f"state must be [slots, {n_heads}, {dim}, {v_dim}], got {tuple(state.shape)}")
+    if max(q_col, f_col) + n_heads * dim > ld or v_col + n_heads * v_dim > ld:
+        raise KernelError("the q, f or v columns lie outside the rows")
+    S = seg_slot.numel()
+    _check(seg_start, "seg_start", torch.int32, (S + 1,))
+    out = torch.empty((T, n_heads * v_dim), dtype=out_dtype, device=proj.device)
+    f = _fn("seq", "ib_gated_recurrence", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 4 +
+            [c_int] * 6 + [c_void_p])
+    _call(f, proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col), lower.data_ptr(), norm_weight.data_ptr(), float(eps),
+          state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, dim, v_dim,
+          int(write_state), dtype_code(out_dtype), _stream())
     return out

@@ -6,6 +6,19 @@ encoded into q and k; k and v go to the request's pages; query head h reads kv h
 kv_heads); score = (q . k) * scale with scale = 1/sqrt(head_dim) unless given; keys j <= p, and
 j > p - window if the layer has a window; softmax in float32; out = residual + ctx Wo^T
 (src/forward.cpp:101-136,208-224; kernels/ops/batch.cu:207-316).
+
+Options beyond that, each a key of the part's spec (absent = off):
+
+``v_head_dim``      values of another size than keys (the value pages and the context rows follow it)
+``filter_taps``     q, k and v each pass a causal filter over time, per channel, directly after the projection:
+                    y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence; the last taps - 1 projected
+                    rows of a request are state beside its pages (``CompositeNeed``)
+``position``        kind "rotary_pairs": adjacent channel pairs over the first ``rotary_dims`` channels of a head
+``value_norm_eps``  every value head is divided by sqrt(mean(v^2) + eps) before it is cached
+``head_gate``       head h's context is multiplied by sigmoid(x Wg^T)[h] before the output product; Wg's rows ride
+                    in the same matrix product as q, k and v
+``names``           local tensor names by role (q, k, v, o, q_bias, k_bias, v_bias, q_filter, k_filter, v_filter, gate)
+                    for checkpoints that call them otherwise
 """
 from __future__ import annotations
 
@@ -16,8 +29,16 @@ import torch
 
 from .. import ops
 from ..config.specs import PartSpec
-from .base import Mixer, PagedKVNeed, build_part, register_mixer
+from .base import CompositeNeed, Mixer, PagedKVNeed, StateNeed, build_part, register_mixer
 from .linear import Linear
+
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+          "q_filter": "q_proj.filter", "k_filter": "k_proj.filter", "v_filter": "v_proj.filter", "gate": "gate_proj.weight"}
+
+
+def _names(spec: PartSpec):
+    return {**_NAMES, **dict(spec.get("names") or {})}
 
 
 @register_mixer("attention")
@@ -28,6 +49,7 @@ class Attention(Mixer):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])
         self.n_heads, self.n_kv, self.head_dim = int(spec["num_heads"]), int(spec["num_kv_heads"]), int(spec["head_dim"])
+        self.v_dim = int(spec.get("v_head_dim") or self.head_dim)
         self.qkv_bias = bool(spec.get("qkv_bias", False))
         self.window = spec.get("window")
         if self.window is not None:
@@ -38,37 +60,100 @@ class Attention(Mixer):
             raise ValueError(f"heads ({self.n_heads}) must be a multiple of kv heads ({self.n_kv})")
         if self.head_dim <= 0 or self.head_dim % 2:
             raise ValueError(f"head_dim must be positive and even, got {self.head_dim}")
-        if self.head_dim > ops.attention_max_head_dim():
-            raise ValueError(f"head_dim {self.head_dim} is beyond what the attention kernels take ({ops.attention_max_head_dim()})")
+        if max(self.head_dim, self.v_dim) > ops.attention_max_head_dim():
+            raise ValueError(f"head_dim {self.head_dim} / {self.v_dim} is beyond what the attention kernels take ({ops.attention_max_head_dim()})")
         scale = spec.get("softmax_scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(self.head_dim))
         pos = spec.get("position")
         self.position = build_part("position", pos, runtime) if pos is not None else None
+        self.taps = int(spec.get("filter_taps") or 0)
+        self.value_norm_eps = spec.get("value_norm_eps")
+        self.head_gate = bool(spec.get("head_gate", False))
+        # anything beyond rotate-and-store goes through the prepare kernel (filter, pair rotation, value norm)
+        self.prepared = (self.taps > 0 or self.value_norm_eps is not None or self.v_dim != self.head_dim or self.head_gate
+                         or getattr(self.position, "layout", "half") == "pairs")
+        if self.prepared:
+            if self.v_dim % 2 or max(self.head_dim, self.v_dim) > ops.qkv_prepare_max_head_dim():
+                raise ValueError(f"the prepare kernel takes even head sizes up to {ops.qkv_prepare_max_head_dim()}, "
+                                 f"got {self.head_dim} / {self.v_dim}")
+            if self.position is not None and getattr(self.position, "layout", None) != "pairs":
+                raise ValueError("filters, value norm, gates and other value sizes go with position kind 'rotary_pairs' (or none)")
+        self.n_qkv = (self.n_heads + self.n_kv) * self.head_dim + self.n_kv * self.v_dim
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
+        self.filter_w = None
 
     @classmethod
     def param_shapes(cls, spec):
         H, nh, nkv, hd = int(spec["hidden_size"]), int(spec["num_heads"]), int(spec["num_kv_heads"]), int(spec["head_dim"])
-        shapes = {"q_proj.weight": (nh * hd, H), "k_proj.weight": (nkv * hd, H), "v_proj.weight": (nkv * hd, H),
-                  "o_proj.weight": (H, nh * hd)}
+        vd = int(spec.get("v_head_dim") or hd)
+        n = _names(spec)
+        shapes = {n["q"]: (nh * hd, H), n["k"]: (nkv * hd, H), n["v"]: (nkv * vd, H), n["o"]: (H, nh * vd)}
         if spec.get("qkv_bias", False):
-            shapes.update({"q_proj.bias": (nh * hd,), "k_proj.bias": (nkv * hd,), "v_proj.bias": (nkv * hd,)})
+            shapes.update({n["q_bias"]: (nh * hd,), n["k_bias"]: (nkv * hd,), n["v_bias"]: (nkv * vd,)})
+        taps = int(spec.get("filter_taps") or 0)
+        if taps > 0:
+            shapes.update({n["q_filter"]: (nh * hd, taps), n["k_filter"]: (nkv * hd, taps), n["v_filter"]: (nkv * vd, taps)})
+        if spec.get("head_gate", False):
+            shapes[n["gate"]] = (nh, H)
         return shapes
 
+    @classmethod
+    def init_params(cls, spec, name, shape, gen):
+        n = _names(spec)
+        if name in (n["q_filter"], n["k_filter"], n["v_filter"]):
+            # taps that keep a channel's scale: about one on the newest tap, small ones before
+            w = 0.3 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
+            w[:, -1] += 1.0
+            return w
+        return super().init_params(spec, name, shape, gen)
+
     def load(self, params):
-        w = torch.cat([params["q_proj.weight"], params["k_proj.weight"], params["v_proj.weight"]], dim=0)
+        n = _names(self.spec)
+        mats = [params[n["q"]], params[n["k"]], params[n["v"]]]
+        if self.head_gate:
+            mats.append(params[n["gate"]])
+        w = torch.cat(mats, dim=0)
+        if self.head_gate and w.shape[0] % 8:
+            # rows of the product's result stay 16-byte aligned for the kernels that read them
+            w = torch.cat([w, torch.zeros(8 - w.shape[0] % 8, w.shape[1], dtype=w.dtype)], dim=0)
         b = None
         if self.qkv_bias:
-            b = torch.cat([params["q_proj.bias"].float(), params["k_proj.bias"].float(), params["v_proj.bias"].float()])
+            b = torch.cat([params[n["q_bias"]].float(), params[n["k_bias"]].float(), params[n["v_bias"]].float()])
+            if w.shape[0] > b.numel():
+                b = torch.cat([b, torch.zeros(w.shape[0] - b.numel())])
         self.qkv = Linear(self.rt, w, b)
-        self.o = Linear(self.rt, params["o_proj.weight"])
+        self.o = Linear(self.rt, params[n["o"]])
+        if self.taps > 0:
+            self.filter_w = torch.cat([params[n["q_filter"]], params[n["k_filter"]], params[n["v_filter"]]], dim=0) \
+                .to(device=self.rt.device, dtype=torch.float32).contiguous()
 
     def cache_need(self):
-        return PagedKVNeed(self.n_kv, self.head_dim, self.window)
+        pages = PagedKVNeed(self.n_kv, self.head_dim, self.window, None if self.v_dim == self.head_dim else self.v_dim)
+        if self.taps > 1:
+            # the last taps - 1 projected rows of the request, in the compute dtype (copies, not sums)
+            return CompositeNeed({"pages": pages, "tails": StateNeed({"qkv": ((self.taps - 1, self.n_qkv), None)})})
+        return pages
+
+    def _context(self, q, cache, table, step):
+        ctx = None
+        if self.rt.fast("attention") and self.v_dim == self.head_dim:
+            from .. import fast_ops
+            ctx = fast_ops.attention(q, cache, table, step, self.n_heads, self.n_kv, self.head_dim, self.window, self.scale)
+        if ctx is None:
+            ctx = ops.attention_plain(q, cache.k, cache.v, table, step.token_seg, step.positions, self.n_heads, self.n_kv,
+                                      self.head_dim, self.window, self.scale, step.status, self.v_dim)
+        return ctx
+
+    def _project_out(self, ctx, residual):
+        if residual is None:
+            return self.o(ctx, out_dtype=torch.float32)
+        return self.o(ctx, residual=residual)
 
     def forward(self, x, step, cache, residual, write_cache=True):
-        qkv = self.qkv(x)                                              # [T, (heads + 2 kv) * head_dim]
+        qkv = self.qkv(x)                                              # [T, (heads + kv) * head_dim + kv * v_dim (+ gates)]
+        if self.prepared:
+            return self._forward_prepared(qkv, step, cache, residual, write_cache)
         table = step.block_tables[cache.group]
         tables = self.position.rotary_tables(self.rt.max_seq_len) if self.position is not None else None
         if self.position is not None and tables is None:
@@ -84,14 +169,28 @@ class Attention(Mixer):
                                                   self.n_heads, self.n_kv, self.head_dim, self.window, self.scale,
                                                   step.max_ctx_len, write_cache)
             if ctx is not None:
-                return self.o(ctx, residual=residual)
+                return self._project_out(ctx, residual)
         q = ops.rope_kv_write(qkv, cos, sin, step.positions, step.token_seg, table, cache.k, cache.v,
                               self.n_heads, self.n_kv, self.head_dim, write_cache, step.status)
-        ctx = None
-        if self.rt.fast("attention"):
-            from .. import fast_ops
-            ctx = fast_ops.attention(q, cache, table, step, self.n_heads, self.n_kv, self.head_dim, self.window, self.scale)
-        if ctx is None:
-            ctx = ops.attention_plain(q, cache.k, cache.v, table, step.token_seg, step.positions,
-                                      self.n_heads, self.n_kv, self.head_dim, self.window, self.scale, step.status)
-        return self.o(ctx, residual=residual)
+        return self._project_out(self._context(q, cache, table, step), residual)
+
+    def _forward_prepared(self, qkv, step, cache, residual, write_cache):
+        """Filter, pair rotation and value norm in one kernel that also fills the pages; then the filter's tails take
+        the step's last projected rows, attention runs over the pages, and the heads are gated."""
+        pages = cache["pages"] if isinstance(cache, dict) else cache
+        tails = cache["tails"]["qkv"] if isinstance(cache, dict) else None
+        table = step.block_tables[pages.group]
+        cos = sin = None
+        n_rot = 0
+        if self.position is not None:
+            cos, sin = self.position.rotary_tables(self.rt.max_seq_len)
+            n_rot = self.position.rotary_dims
+        q = ops.qkv_prepare(qkv, self.filter_w, tails, cos, sin, n_rot, self.value_norm_eps is not None,
+                            float(self.value_norm_eps or 0.0), step, table, pages.k, pages.v, self.n_heads, self.n_kv,
+                            self.head_dim, self.v_dim, write_cache)
+        if tails is not None and write_cache:
+            ops.filter_tail_update(qkv, 0, tails, step.seg_start, step.seg_slot)
+        ctx = self._context(q, pages, table, step)
+        if self.head_gate:
+            ops.head_gate(ctx, qkv, self.n_qkv, self.n_heads, self.v_dim)
+        return self._project_out(ctx, residual)

@@ -26,14 +26,28 @@ class PagedKVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: all positions stay; n: only the last n are ever read
+    v_head_dim: Optional[int] = None  # size of a value where it differs from a key's (None: head_dim)
+
+    @property
+    def value_dim(self) -> int:
+        return int(self.v_head_dim or self.head_dim)
 
 
 @dataclass(frozen=True)
 class StateNeed:
     """A fixed-size state per request, zeroed when the request is admitted.
 
-    shapes maps a state tensor's name to (shape without the slot dimension, torch dtype)."""
-    shapes: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]]
+    shapes maps a state tensor's name to (shape without the slot dimension, torch dtype); a dtype of None stands
+    for the model's compute dtype (copies of activations, as opposed to sums that must stay float32)."""
+    shapes: Mapping[str, Tuple[Tuple[int, ...], Optional[torch.dtype]]]
+
+
+@dataclass(frozen=True)
+class CompositeNeed:
+    """Several needs of one cache entry, by name: a mixer that keeps pages AND a fixed-size state (attention whose
+    projections pass a filter over time), or mixers that run side by side on one input. The cache manager gives such
+    an entry a dict ``name -> view`` of the same shape (nested where a need is itself composite)."""
+    parts: Mapping[str, Any]         # name -> PagedKVNeed | StateNeed | CompositeNeed | None
 
 
 # ----------------------------------------------------------------------------- interfaces
@@ -106,13 +120,14 @@ class Mixer(Part):
     accepts_deferred_norm = False    # True: forward() may get a DeferredNorm as x
 
     def cache_need(self):
-        """PagedKVNeed, StateNeed or None."""
+        """PagedKVNeed, StateNeed, CompositeNeed or None."""
         return None
 
     def forward(self, x: torch.Tensor, step: "StepContext", cache: Any, residual: torch.Tensor,
                 write_cache: bool = True) -> torch.Tensor:
         """x: normalised rows [T, hidden] in the compute dtype; residual: float32 [T, hidden].
-        Returns residual + mixer(x) as float32 [T, hidden] (it may overwrite ``residual``).
+        Returns residual + mixer(x) as float32 [T, hidden] (it may overwrite ``residual``); with ``residual`` None,
+        mixer(x) alone as float32 (for blocks that weigh or gate a sublayer's result before they add it).
         ``cache`` is what the cache manager made for this part's need: a ``PagedKVView``,
         a dict of state tensors [slots, ...], or None."""
         raise NotImplementedError
@@ -122,7 +137,17 @@ class FeedForward(Part):
     accepts_deferred_norm = False
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        """Returns residual + feed_forward(x), float32 [T, hidden] (may overwrite ``residual``)."""
+        """Returns residual + feed_forward(x), float32 [T, hidden] (may overwrite ``residual``); with ``residual``
+        None, feed_forward(x) alone as float32."""
+        raise NotImplementedError
+
+
+class Gate(Part):
+    """Multipliers for sublayer results, computed from the rows the sublayers read."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: normalised rows [T, hidden] in the compute dtype -> float32 gate logits [T, n * hidden], n the number
+        of sublayers this part gates; the block's sum applies the squashing function."""
         raise NotImplementedError
 
 
@@ -173,7 +198,7 @@ class Block:
 # ----------------------------------------------------------------------------- registries
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
-                                           "embedding": {}, "head": {}}
+                                           "embedding": {}, "head": {}, "gate": {}}
 
 
 def _register(family: str, name: str) -> Callable[[type], type]:
@@ -192,6 +217,7 @@ def register_position(name: str): return _register("position", name)
 def register_block(name: str): return _register("block", name)
 def register_embedding(name: str): return _register("embedding", name)
 def register_head(name: str): return _register("head", name)
+def register_gate(name: str): return _register("gate", name)
 
 
 def unregister(family: str, name: str) -> None:

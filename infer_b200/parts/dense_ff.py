@@ -1,0 +1,49 @@
+"""Dense feed-forward with one hidden layer: out = residual + act(x Wup^T) Wdown^T, no biases.
+
+``activation``: "gelu_tanh" is 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  ``names`` renames the two matrices
+(roles up, down).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.specs import PartSpec
+from .base import FeedForward, register_feed_forward
+from .linear import Linear
+
+_ACTIVATIONS = {"gelu_tanh": ops.gelu_tanh}
+_NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
+
+
+@register_feed_forward("dense")
+class DenseFeedForward(FeedForward):
+    accepts_deferred_norm = True
+
+    def __init__(self, spec: PartSpec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        if self.hidden <= 0 or self.inter <= 0:
+            raise ValueError("a dense feed-forward needs positive sizes")
+        act = spec.get("activation", "gelu_tanh")
+        if act not in _ACTIVATIONS:
+            raise ValueError(f"activation {act!r} is not among {sorted(_ACTIVATIONS)}")
+        self.activation = _ACTIVATIONS[act]
+        self.up = self.down = None
+
+    @classmethod
+    def param_shapes(cls, spec):
+        H, I = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        n = {**_NAMES, **dict(spec.get("names") or {})}
+        return {n["up"]: (I, H), n["down"]: (H, I)}
+
+    def load(self, params):
+        n = {**_NAMES, **dict(self.spec.get("names") or {})}
+        self.up = Linear(self.rt, params[n["up"]])
+        self.down = Linear(self.rt, params[n["down"]])
+
+    def forward(self, x, residual):
+        act = self.activation(self.up(x))
+        if residual is None:
+            return self.down(act, out_dtype=torch.float32)
+        return self.down(act, residual=residual)

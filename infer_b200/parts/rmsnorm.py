@@ -1,5 +1,6 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w; eps inside the root, added after the mean; no mean
-subtraction, no bias, the weight multiplies as it is (src/forward.cpp:21-31, kernels/ops/rmsnorm.cu:9-28)."""
+subtraction, no bias, the weight multiplies as it is (src/forward.cpp:21-31, kernels/ops/rmsnorm.cu:9-28).
+``weight_name`` in the spec renames the one tensor (default "weight") under the part's prefix."""
 from __future__ import annotations
 
 from typing import Optional
@@ -27,14 +28,14 @@ class RMSNorm(Norm):
 
     @classmethod
     def param_shapes(cls, spec):
-        return {"weight": (int(spec["size"]),)}
+        return {str(spec.get("weight_name", "weight")): (int(spec["size"]),)}
 
     @classmethod
     def init_params(cls, spec, name, shape, gen):
         return 1.0 + 0.1 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
 
     def load(self, params):
-        self.weight = params["weight"].to(device=self.rt.device, dtype=torch.float32).contiguous()
+        self.weight = params[str(self.spec.get("weight_name", "weight"))].to(device=self.rt.device, dtype=torch.float32).contiguous()
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -1,0 +1,62 @@
+"""Two mixers that read the same rows; the result is a * first(x) + b * second(x).
+
+The spec holds the two mixers' own specs under ``first`` and ``second`` (family "mixer", any registered kinds; their
+prefixes are relative to this part's) and the two constants.  Each keeps its own pages or state: the part's need is
+the two needs by name.  Tensors are declared and loaded through the two mixers' classes.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import PartSpec
+from .base import CompositeNeed, Mixer, build_part, part_class, register_mixer
+
+_SIDES = ("first", "second")
+
+
+@register_mixer("side_by_side")
+class SideBySide(Mixer):
+    def __init__(self, spec: PartSpec, runtime):
+        super().__init__(spec, runtime)
+        self.sides = {s: build_part("mixer", spec[s], runtime) for s in _SIDES}
+        self.scales = {"first": float(spec.get("first_scale", 1.0)), "second": float(spec.get("second_scale", 1.0))}
+        self.graph_safe = all(getattr(m, "graph_safe", True) for m in self.sides.values())
+
+    @classmethod
+    def param_shapes(cls, spec):
+        shapes = {}
+        for s in _SIDES:
+            sub = spec[s]
+            for local, shape in part_class("mixer", sub.kind).param_shapes(sub).items():
+                shapes[sub.prefix + local] = shape
+        return shapes
+
+    @classmethod
+    def init_params(cls, spec, name, shape, gen):
+        for s in _SIDES:
+            sub = spec[s]
+            sub_cls = part_class("mixer", sub.kind)
+            if name.startswith(sub.prefix) and name[len(sub.prefix):] in sub_cls.param_shapes(sub):
+                return sub_cls.init_params(sub, name[len(sub.prefix):], shape, gen)
+        return super().init_params(spec, name, shape, gen)
+
+    def load(self, params):
+        for s, m in self.sides.items():
+            sub = self.spec[s]
+            m.load({local: params[sub.prefix + local] for local in type(m).param_shapes(sub)})
+
+    def cache_need(self):
+        return CompositeNeed({s: m.cache_need() for s, m in self.sides.items()})
+
+    def forward_sides(self, x, step, cache, write_cache=True):
+        """(first(x), second(x)) as float32, and the two constants: for a block whose sum applies them."""
+        a = self.sides["first"].forward(x, step, cache["first"], None, write_cache)
+        b = self.sides["second"].forward(x, step, cache["second"], None, write_cache)
+        return a, b, self.scales["first"], self.scales["second"]
+
+    def forward(self, x, step, cache, residual, write_cache=True):
+        from .. import ops
+        a, b, sa, sb = self.forward_sides(x, step, cache, write_cache)
+        if residual is None:
+            residual = torch.zeros_like(a)
+        return ops.gated_sum(residual, None, a, sa, b, sb)

@@ -4,7 +4,8 @@
 h[t, :] = float32(table[ids[t], :]), optionally times a constant ``scale`` (src/forward.cpp:181-187 has none);
 logits = x . W^T without bias, W being the head's own matrix or, when tied, the token table itself
 (src/forward.cpp:246-257, src/model.h:52). An architecture whose ends do more (a soft cap on the logits, a bias)
-registers its own ``Embedding`` / ``Head`` kinds; the model only calls ``forward``.
+registers its own ``Embedding`` / ``Head`` kinds; the model only calls ``forward``. ``weight_name`` in either spec
+renames the part's one tensor (default "weight") under its prefix.
 """
 from __future__ import annotations
 
@@ -29,11 +30,11 @@ class TokenTable(Embedding):
 
     @classmethod
     def param_shapes(cls, spec):
-        return {"weight": (int(spec["vocab_size"]), int(spec["hidden_size"]))}
+        return {str(spec.get("weight_name", "weight")): (int(spec["vocab_size"]), int(spec["hidden_size"]))}
 
     def load(self, params):
         # The table is read row by row; it keeps the compute dtype of the matrices (a tied head multiplies by it).
-        self.weight = params["weight"].to(device=self.rt.device, dtype=self.rt.dtype).contiguous()
+        self.weight = params[str(self.spec.get("weight_name", "weight"))].to(device=self.rt.device, dtype=self.rt.dtype).contiguous()
 
     def table(self):
         return self.weight
@@ -53,11 +54,11 @@ class LinearHead(Head):
 
     @classmethod
     def param_shapes(cls, spec):
-        return {} if spec.get("tied", False) else {"weight": (int(spec["vocab_size"]), int(spec["hidden_size"]))}
+        return {} if spec.get("tied", False) else {str(spec.get("weight_name", "weight")): (int(spec["vocab_size"]), int(spec["hidden_size"]))}
 
     def load(self, params):
         if not self.tied:
-            self.linear = Linear(self.rt, params["weight"])
+            self.linear = Linear(self.rt, params[str(self.spec.get("weight_name", "weight"))])
 
     def tie(self, embedding):
         if not self.tied:

@@ -64,7 +64,7 @@ def load_weights(model_dir: str, spec: ModelSpec) -> Dict[str, torch.Tensor]:
             for n in f.names():
                 have.setdefault(n, f)
         missing = [n for n in sorted(want) if n not in have]
-        unexpected = [n for n in sorted(have) if n not in want]
+        unexpected = [n for n in sorted(have) if n not in want and n not in spec.optional_tensors]
         wrong = [(n, want[n][0], have[n].shape(n)) for n in sorted(want)
                  if n in have and tuple(have[n].shape(n)) != tuple(want[n][0])]
         if missing or unexpected or wrong:
@@ -78,7 +78,7 @@ def load_weights(model_dir: str, spec: ModelSpec) -> Dict[str, torch.Tensor]:
 def check_weights(weights: Mapping[str, torch.Tensor], spec: ModelSpec, where: str = "(in memory)") -> None:
     want = expected_tensors(spec)
     missing = [n for n in sorted(want) if n not in weights]
-    unexpected = [n for n in sorted(weights) if n not in want]
+    unexpected = [n for n in sorted(weights) if n not in want and n not in spec.optional_tensors]
     wrong = [(n, want[n][0], tuple(weights[n].shape)) for n in sorted(want)
              if n in weights and tuple(weights[n].shape) != tuple(want[n][0])]
     if missing or unexpected or wrong:
