@@ -18,6 +18,10 @@ recurrent_side (per head, state S of [dim, vdim] starting at zero):
     f_t = l + (1 - l) * sigmoid(F n_t + c),   q_t = silu(Q n_t),   v_t = V n_t
     S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,   o_t = S_t^T q_t
 then o_t is rms-normalised per head with a weight shared by the heads, heads are joined and projected.
+
+``rounding``: None computes exactly. ``torch.bfloat16`` rounds activations where a bfloat16 serving path stores them
+(normalised rows, projected and prepared q/k/v, contexts, feed-forward activations, the recurrence's normalised
+output), which gives the size of the rounding noise such a path must have.
 """
 from __future__ import annotations
 
@@ -27,6 +31,10 @@ from typing import Dict, List, Mapping, Optional, Sequence
 import torch
 
 F = torch.float64
+
+
+def _rnd(x: torch.Tensor, rounding) -> torch.Tensor:
+    return x if rounding is None else x.to(rounding).to(x.dtype)
 
 
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -89,18 +97,22 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     return out
 
 
-def attention_side(n: torch.Tensor, W: Mapping[str, torch.Tensor], pre: str, cfg: Mapping, eps: float) -> torch.Tensor:
-    H, G, d, dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
+def attention_side(n: torch.Tensor, W: Mapping[str, torch.Tensor], pre: str, cfg: Mapping, eps: float, rounding=None) -> torch.Tensor:
+    H, d = cfg["heads"], cfg["dim"]
+    G = cfg["kv_heads"] if cfg.get("kv_heads") is not None else H
+    dv = cfg["vdim"] if cfg.get("vdim") is not None else d
     T = n.shape[0]
-    q = short_filter(linear(n, W[pre + "q"]), W[pre + "q.conv"]).view(T, H, d)
-    k = short_filter(linear(n, W[pre + "k"]), W[pre + "k.conv"]).view(T, G, d)
-    v = short_filter(linear(n, W[pre + "v"]), W[pre + "v.conv"]).view(T, G, dv)
-    q = rotate_pairs(q, cfg["rot"]["dims"], cfg["rot"]["base"])
-    k = rotate_pairs(k, cfg["rot"]["dims"], cfg["rot"]["base"])
-    v = rms(v, eps)
-    o = causal_attention(q, k, v, float(cfg["scale"]))
-    gate = torch.sigmoid(linear(n, W[pre + "g"]))                  # [T, H]
-    o = o * gate[:, :, None]
+    q, k, v = (_rnd(linear(n, W[pre + x]), rounding) for x in ("q", "k", "v"))
+    if cfg.get("conv"):
+        q, k, v = (short_filter(u, W[pre + x + ".conv"]) for u, x in ((q, "q"), (k, "k"), (v, "v")))
+    q, k, v = q.view(T, H, d), k.view(T, G, d), v.view(T, G, dv)
+    if cfg.get("rot") is not None and cfg["rot"]["dims"]:
+        q = rotate_pairs(q, cfg["rot"]["dims"], cfg["rot"]["base"])
+        k = rotate_pairs(k, cfg["rot"]["dims"], cfg["rot"]["base"])
+    q, k, v = _rnd(q, rounding), _rnd(k, rounding), _rnd(rms(v, eps), rounding)
+    o = _rnd(causal_attention(q, k, v, float(cfg["scale"])), rounding)
+    gate = torch.sigmoid(_rnd(linear(n, W[pre + "g"]), rounding))   # [T, H]
+    o = _rnd(o * gate[:, :, None], rounding)
     return linear(o.reshape(T, H * dv), W[pre + "o"])
 
 
@@ -115,48 +127,50 @@ def gated_recurrence(q: torch.Tensor, f: torch.Tensor, v: torch.Tensor, state: O
     return o, S
 
 
-def recurrent_side(n: torch.Tensor, W: Mapping[str, torch.Tensor], pre: str, cfg: Mapping, eps: float) -> torch.Tensor:
-    H, d, dv = cfg["heads"], cfg["dim"], cfg["vdim"]
+def recurrent_side(n: torch.Tensor, W: Mapping[str, torch.Tensor], pre: str, cfg: Mapping, eps: float, rounding=None) -> torch.Tensor:
+    H, d = cfg["heads"], cfg["dim"]
+    dv = cfg["vdim"] if cfg.get("vdim") is not None else d
     T = n.shape[0]
     q = torch.nn.functional.silu(linear(n, W[pre + "q"])).view(T, H, d)
     v = linear(n, W[pre + "v"]).view(T, H, dv)
     low = W[pre + "lower"].to(F)
     f = (low + (1.0 - low) * torch.sigmoid(linear(n, W[pre + "f"], W[pre + "f.b"]))).view(T, H, d)
     o, _ = gated_recurrence(q, f, v)
-    o = rms(o, eps) * W[pre + "norm"].to(F)
+    o = _rnd(rms(o, eps) * W[pre + "norm"].to(F), rounding)
     return linear(o.reshape(T, H * dv), W[pre + "o"])
 
 
-def feed_forward(n: torch.Tensor, W: Mapping[str, torch.Tensor], pre: str) -> torch.Tensor:
-    return linear(gelu_tanh(linear(n, W[pre + "up"])), W[pre + "down"])
+def feed_forward(n: torch.Tensor, W: Mapping[str, torch.Tensor], pre: str, rounding=None) -> torch.Tensor:
+    return linear(_rnd(gelu_tanh(_rnd(linear(n, W[pre + "up"]), rounding)), rounding), W[pre + "down"])
 
 
-def layer(x: torch.Tensor, W: Mapping[str, torch.Tensor], i: int, lcfg: Mapping, eps: float) -> torch.Tensor:
+def layer(x: torch.Tensor, W: Mapping[str, torch.Tensor], i: int, lcfg: Mapping, eps: float, rounding=None) -> torch.Tensor:
     if lcfg["type"] != "parallel":
         raise ValueError(f"layer type {lcfg['type']!r}")
     p = f"l{i}."
-    n = rms_weighted(x, W[p + "norm1"], eps)
+    n = _rnd(rms_weighted(x, W[p + "norm1"], eps), rounding)
     m = lcfg["mixer"]
-    mix = float(m["left_scale"]) * attention_side(n, W, p + "mix.left.", m["left"], eps) + \
-        float(m["right_scale"]) * recurrent_side(n, W, p + "mix.right.", m["right"], eps)
+    mix = float(m["left_scale"]) * attention_side(n, W, p + "mix.left.", m["left"], eps, rounding) + \
+        float(m["right_scale"]) * recurrent_side(n, W, p + "mix.right.", m["right"], eps, rounding)
     y = torch.sigmoid(linear(n, W[p + "rg1"], W[p + "rg1.b"])) * mix
     if lcfg.get("mlp") is not None:
         if lcfg["mlp"]["kind"] != "dense":
             raise ValueError("feed-forward kind")
-        y = y + torch.sigmoid(linear(n, W[p + "rg2"], W[p + "rg2.b"])) * feed_forward(n, W, p + "mlp.")
+        y = y + torch.sigmoid(linear(n, W[p + "rg2"], W[p + "rg2.b"])) * feed_forward(n, W, p + "mlp.", rounding)
     return x + y
 
 
-def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[List] = None) -> torch.Tensor:
+def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[List] = None,
+            rounding=None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence. ``layers_out`` collects the stream after every layer."""
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     x = W["embed"].to(F)[ids] * float(cfg["embedding"]["scale"])
     eps = float(cfg["norm"]["eps"])
     for i, lcfg in enumerate(cfg["layers"]):
-        x = layer(x, W, i, lcfg, eps)
+        x = layer(x, W, i, lcfg, eps, rounding)
         if layers_out is not None:
             layers_out.append(x.clone())
-    return linear(rms_weighted(x, W["final.norm"], eps), W["head"])
+    return linear(_rnd(rms_weighted(x, W["final.norm"], eps), rounding), W["head"])
 
 
 def greedy(cfg: Mapping, W: Mapping[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:
