@@ -2,6 +2,7 @@
 random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L] [--impl reference]
+    python bench.py --design ruvenex [--sizes 1.5b|7b] [--layers L]     (another design beside Qwen2 at equal sizes)
 
 Prints ONE JSON line. "value" is decoded tokens per second of the step function, timed on the device with CUDA
 events around K decode steps of a batch of 8 requests whose 2,048-token contexts already lie in the paged cache
@@ -31,6 +32,8 @@ def _preset(name):
 
 
 SIZES = {"1.5b": _preset("qwen2.5-1.5b"), "7b": _preset("qwen2.5-7b"), "14b": _preset("qwen2.5-14b")}
+# Other designs at the same layer sizes (width, heads, feed-forward), for --design.
+DESIGNS = {"ruvenex": {"1.5b": "ruvenex-1.5b", "7b": "ruvenex-7b"}}
 CONFIG = SIZES["1.5b"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -114,7 +117,8 @@ def build_engine(n_layers, batch, context, steps_total, dtype="bfloat16"):
     from infer_b200.engine import Engine
     from infer_b200.weights import random_weights
     import infer_b200.models  # noqa: F401
-    cfg = dict(CONFIG, num_hidden_layers=n_layers)
+    cfg = dict(CONFIG, layers=CONFIG["layers"][:n_layers]) if isinstance(CONFIG.get("layers"), list) \
+        else dict(CONFIG, num_hidden_layers=n_layers)
     arch, typed = parse_config(cfg)
     spec = arch.to_spec(typed)
     W = random_weights(spec, 0, torch.bfloat16, device="cuda")
@@ -153,8 +157,9 @@ def decode_bytes(eng, batch, context_mid):
     head_w = getattr(getattr(eng.model.head, "linear", None), "weight", None)
     if table is not None and (head_w is None or head_w.data_ptr() != table.data_ptr()):
         w -= table.numel() * item - batch * spec.hidden_size * item         # an untied table is read row by row only
-    kv = sum(2 * len(g.cache_ids) * g.need.num_kv_heads * g.need.head_dim * item for g in eng.cache.groups)
-    return w + batch * context_mid * kv, w, kv
+    kv = sum(len(g.cache_ids) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * item for g in eng.cache.groups)
+    state = sum(t[0].numel() * t.element_size() for tensors in eng.cache.state.values() for t in tensors.values())
+    return w + batch * (context_mid * kv + 2 * state), w, kv          # a request's fixed-size state is read and written
 
 
 def time_decode(eng, batch, context, steps, warmup, kernel_counter):
@@ -357,6 +362,52 @@ def reference_arm(args):
     return 0
 
 
+def design_flops(cfg, T):
+    """Arithmetic of a prompt of T tokens through a model of --design's configuration (matrix products, attention
+    scores and sums, the recurrence's state updates and read-outs), logits at the last place only."""
+    W, total = cfg["width"], 0.0
+    for l in cfg["layers"]:
+        a, r = l["mixer"]["left"], l["mixer"]["right"]
+        n_out = (a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"] + a["heads"] + 2 * r["heads"] * r["dim"] + r["heads"] * r["vdim"]
+        n_out += W * (2 if l["mlp"] else 1) + (l["mlp"]["ff"] if l["mlp"] else 0)
+        n_in = a["heads"] * a["vdim"] + r["heads"] * r["vdim"] + (l["mlp"]["ff"] if l["mlp"] else 0)
+        total += 2 * T * W * (n_out + n_in)
+        total += 2 * a["heads"] * (a["dim"] + a["vdim"]) * T * (T + 1) / 2
+        total += T * r["heads"] * r["dim"] * r["vdim"] * 5
+    return total + 2 * W * cfg["vocab"]
+
+
+def design_arm(args, pk):
+    """--design: decode at --batch and --context and a prompt of 2,048 tokens, for the named design and for Qwen2 at
+    the same layer sizes, each with the same number of layers; one JSON line, the default workload untouched."""
+    import torch
+    from infer_b200 import ops
+    global CONFIG
+    out = {"design": args.design, "sizes": args.sizes, "batch": args.batch, "context": args.context, "dtype": "bf16",
+           "data": "synthetic: random weights, random cache contents, fixed token ids", "peaks": pk["source"], "models": {}}
+    T = 2048
+    for label, preset in ((args.design, _preset(DESIGNS[args.design][args.sizes])), ("qwen2", SIZES[args.sizes])):
+        CONFIG = preset
+        n_all = len(preset["layers"]) if isinstance(preset.get("layers"), list) else preset["num_hidden_layers"]
+        n_layers = args.layers or n_all
+        eng = build_engine(n_layers, args.batch, max(args.context, T), 2 * (args.steps + args.warmup) + 64)
+        ms_step, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, ops.kernel_launches)
+        nbytes, wbytes, _ = decode_bytes(eng, args.batch, args.context + args.warmup + args.steps // 2)
+        ms_p = time_prefill(eng, T, 5, 3)
+        fl = design_flops(dict(preset, layers=preset["layers"][:n_layers]), T) if label != "qwen2" else prefill_flops(preset, n_layers, T)
+        out["models"][label] = {
+            "layers": n_layers, "weights_gb": round(wbytes / 1e9, 3),
+            "decode_tok_s": round(args.batch * 1e3 / ms_step, 1), "decode_ms_per_step": round(ms_step, 4),
+            "decode_us_per_layer": round(ms_step * 1e3 / n_layers, 2), "decode_launches_per_step": launches // max(1, args.steps),
+            "decode_hbm_frac": round(nbytes / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+            "prefill_tok_s": round(T * 1e3 / ms_p, 1), "prefill_ms": round(ms_p, 3), "prefill_us_per_layer": round(ms_p * 1e3 / n_layers, 1),
+            "prefill_bf16_frac": round(fl / (ms_p * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        del eng
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -367,6 +418,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all of them)")
     ap.add_argument("--sizes", default="1.5b", choices=sorted(SIZES), help="layer sizes: Qwen2.5-1.5B (the default), 7B or 14B")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
+                    help="decode and prefill throughput of another design beside Qwen2 at the same layer sizes (--sizes 1.5b or 7b)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--points", default="1,64", help="batch sizes of the further decode points (default 1,64)")
     ap.add_argument("--workload", default="decode", choices=["decode", "serve"],
@@ -388,6 +441,11 @@ def main():
     import torch
     from infer_b200 import ops
     pk = peaks()
+    if args.design:
+        if args.sizes not in DESIGNS[args.design]:
+            print(f"bench.py: --design {args.design} has sizes {sorted(DESIGNS[args.design])}")
+            return 2
+        return design_arm(args, pk)
     n_layers = args.layers or CONFIG["num_hidden_layers"]
     total_steps = args.steps + args.warmup
     cfg = CONFIG

@@ -116,12 +116,12 @@ class Attention(Mixer):
         w = torch.cat(mats, dim=0)
         if self.head_gate and w.shape[0] % 8:
             # rows of the product's result stay 16-byte aligned for the kernels that read them
-            w = torch.cat([w, torch.zeros(8 - w.shape[0] % 8, w.shape[1], dtype=w.dtype)], dim=0)
+            w = torch.cat([w, torch.zeros(8 - w.shape[0] % 8, w.shape[1], dtype=w.dtype, device=w.device)], dim=0)
         b = None
         if self.qkv_bias:
             b = torch.cat([params[n["q_bias"]].float(), params[n["k_bias"]].float(), params[n["v_bias"]].float()])
             if w.shape[0] > b.numel():
-                b = torch.cat([b, torch.zeros(w.shape[0] - b.numel())])
+                b = torch.cat([b, torch.zeros(w.shape[0] - b.numel(), device=b.device)])
         self.qkv = Linear(self.rt, w, b)
         self.o = Linear(self.rt, params[n["o"]])
         if self.taps > 0:

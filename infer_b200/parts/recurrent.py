@@ -74,7 +74,8 @@ class GatedLinearRecurrence(Mixer):
         n = _names(self.spec)
         w = torch.cat([params[n["q"]], params[n["f"]], params[n["v"]]], dim=0)
         nq = self.n_heads * self.dim
-        b = torch.cat([torch.zeros(nq), params[n["f_bias"]].float(), torch.zeros(self.n_heads * self.v_dim)])
+        fb = params[n["f_bias"]].float()
+        b = torch.cat([torch.zeros(nq, device=fb.device), fb, torch.zeros(self.n_heads * self.v_dim, device=fb.device)])
         self.proj = Linear(self.rt, w, b)
         self.o = Linear(self.rt, params[n["o"]])
         self.lower = params[n["lower"]].to(device=self.rt.device, dtype=torch.float32).contiguous()
