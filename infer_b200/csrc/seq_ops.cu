@@ -228,89 +228,155 @@ __global__ void gated_sum_kernel(const float* x, const float* __restrict__ gates
 //   S <- diag(f) S + (1 - f) v^T          S [d, dv] float, per request and head, kept in `state` between steps
 //   o = S^T q,  out = o / sqrt(mean(o^2) + eps) * norm_w      (per head; norm_w [dv] shared by the heads)
 // Rows `proj` are float [tokens, ld] with q_raw at q_col, f_raw at f_col (both heads * d wide) and v at v_col
-// (heads * dv wide).  One CTA per (segment, head) walks over the segment's tokens in order.  Thread (kg, col) keeps
-// rows kg * kpt .. of column col of S in registers; tokens are staged `chunk` at a time in shared memory, the
-// column sums over kg are added in ascending order.
-constexpr int REC_MAXK = 32, REC_THREADS = 512;
+// (heads * dv wide).
+//
+// A CTA walks over the tokens of one segment, in order, for one head and `cb` of its columns. Thread (kg, col) keeps
+// MAXK rows of column col of S in registers (rows kg * kpt ..; kpt <= MAXK, the rest padded with zeros); tokens are
+// staged `chunk` at a time in shared memory as [token][kg][MAXK], so that the inner loop is 16-byte loads and three
+// floating-point operations per state element; the column sums over kg are added in ascending order.
+// Two ways to run it, with the same arithmetic per element and therefore the same bits:
+//   * one CTA per (segment, head) over all columns, gates computed while staging, the head's norm at the end of every
+//     chunk: one launch, for steps of a few tokens per request;
+//   * a grid over column blocks as well, for prompt portions: the chain over the tokens is the critical path, so the
+//     columns of a head are spread over many SMs. The gates are then computed once by recurrence_gates_kernel (in
+//     place, instead of once per column block), the CTAs write the bare o, and head_norm_kernel normalises.
+__device__ __forceinline__ float silu_value(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float forget_value(float low, float x) { return __fmaf_rn(1.0f - low, sigmoidf_(x), low); }
 
+__global__ void recurrence_gates_kernel(float* __restrict__ proj, int64_t ld, int q_col, int f_col,
+                                        const float* __restrict__ lower, int64_t n_tokens, int width) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * width) return;
+    const int64_t t = i / width;
+    const int c = int(i - t * width);
+    float* row = proj + t * ld;
+    row[q_col + c] = silu_value(row[q_col + c]);
+    row[f_col + c] = forget_value(lower[c], row[f_col + c]);
+}
+
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w, lanes striding over the columns.
 template <typename TOut>
-__global__ void __launch_bounds__(REC_THREADS)
+__global__ void head_norm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                 TOut* __restrict__ out, int64_t n_rows, int dv) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float* x = o + r * dv;
+    float ss = 0.0f;
+    for (int j = lane; j < dv; j += 32) ss = fmaf(x[j], x[j], ss);
+    ss = ib::warp_sum(ss);
+    const float f = rsqrtf(ss / float(dv) + eps);
+    for (int j = lane; j < dv; j += 32) out[r * dv + j] = ib::from_f32<TOut>(x[j] * f * w[j]);
+}
+
+template <typename TOut, int MAXK>
+__global__ void __launch_bounds__(MAXK > 8 ? 512 : 1024)
 gated_recurrence_kernel(const float* __restrict__ proj, int64_t ld, int q_col, int f_col, int v_col,
                         const float* __restrict__ lower, const float* __restrict__ norm_w, float eps,
                         float* __restrict__ state, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
-                        TOut* __restrict__ out, int n_heads, int d, int dv, int ks, int kpt, int chunk, int write_state) {
+                        TOut* __restrict__ out, float* __restrict__ raw_out, int n_heads, int d, int dv, int ks, int kpt,
+                        int cb, int chunk, int activated, int write_state) {
     ib::pdl_wait();
-    extern __shared__ float sm[];
-    float* qs = sm;                          // [chunk][d]
-    float* fs = qs + chunk * d;              // [chunk][d]
-    float* vs = fs + chunk * d;              // [chunk][dv]
-    float* part = vs + chunk * dv;           // [chunk][ks][dv]
-    float* os = part + chunk * ks * dv;      // [chunk][dv]
+    extern __shared__ __align__(16) float sm[];
+    const int kstride = ks * MAXK;               // staged rows: [kg][MAXK], zero beyond the head's d rows
+    float* qs = sm;                              // [chunk][ks][MAXK]
+    float* fs = qs + chunk * kstride;
+    float* ws = fs + chunk * kstride;            // 1 - f
+    float* vs = ws + chunk * kstride;            // [chunk][cb]
+    float* part = vs + chunk * cb;               // [chunk][ks][cb]
+    float* os = part + chunk * ks * cb;          // [chunk][cb]
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
-    const int col = tid % dv, kg = tid / dv;
+    const int col_l = tid % cb, kg = tid / cb;
+    const int col = blockIdx.z * cb + col_l;
+    const bool active = kg < ks && col < dv;
     const int k0 = kg * kpt;
-    const int nk = kg < ks ? max(0, min(kpt, d - k0)) : 0;
+    const int nk = active ? max(0, min(kpt, d - k0)) : 0;
     const int64_t t0 = seg_start[s];
     const int len = int(seg_start[s + 1] - t0);
     float* S_g = state + (int64_t(seg_slot[s]) * n_heads + h) * int64_t(d) * dv;
-    float S[REC_MAXK];
+    float S[MAXK];
 #pragma unroll
-    for (int kk = 0; kk < REC_MAXK; kk++) S[kk] = kk < nk ? S_g[int64_t(k0 + kk) * dv + col] : 0.0f;
+    for (int kk = 0; kk < MAXK; kk++) S[kk] = kk < nk ? S_g[int64_t(k0 + kk) * dv + col] : 0.0f;
 
     for (int c0 = 0; c0 < len; c0 += chunk) {
         const int n = min(chunk, len - c0);
-        for (int idx = tid; idx < n * d; idx += blockDim.x) {
-            const int c = idx / d, k = idx - c * d;
-            const float* row = proj + (t0 + c0 + c) * ld;
-            const float qr = row[q_col + h * d + k];
-            qs[idx] = qr / (1.0f + expf(-qr));
-            const float lo = lower[h * d + k];
-            fs[idx] = lo + (1.0f - lo) * sigmoidf_(row[f_col + h * d + k]);
+        for (int idx = tid; idx < n * kstride; idx += blockDim.x) {
+            const int c = idx / kstride, r = idx - c * kstride;
+            const int g = r / MAXK, kk = r - g * MAXK;
+            const int k = g * kpt + kk;
+            float q = 0.0f, f = 0.0f, w = 0.0f;
+            if (kk < kpt && k < d) {
+                const float* row = proj + (t0 + c0 + c) * ld;
+                q = row[q_col + h * d + k];
+                f = row[f_col + h * d + k];
+                if (!activated) {
+                    q = silu_value(q);
+                    f = forget_value(lower[h * d + k], f);
+                }
+                w = 1.0f - f;
+            }
+            qs[idx] = q;
+            fs[idx] = f;
+            ws[idx] = w;
         }
-        for (int idx = tid; idx < n * dv; idx += blockDim.x) {
-            const int c = idx / dv, j = idx - c * dv;
-            vs[idx] = proj[(t0 + c0 + c) * ld + v_col + h * dv + j];
+        for (int idx = tid; idx < n * cb; idx += blockDim.x) {
+            const int c = idx / cb, j = blockIdx.z * cb + (idx - c * cb);
+            vs[idx] = j < dv ? proj[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
         }
         __syncthreads();
-        if (kg < ks) {
+        if (active) {
             for (int c = 0; c < n; c++) {
-                const float v = vs[c * dv + col];
-                const float* fr = fs + c * d + k0;
-                const float* qr = qs + c * d + k0;
+                const float v = vs[c * cb + col_l];
+                const float4* f4 = reinterpret_cast<const float4*>(fs + c * kstride + kg * MAXK);
+                const float4* w4 = reinterpret_cast<const float4*>(ws + c * kstride + kg * MAXK);
+                const float4* q4 = reinterpret_cast<const float4*>(qs + c * kstride + kg * MAXK);
                 float acc = 0.0f;
 #pragma unroll
-                for (int kk = 0; kk < REC_MAXK; kk++) {
-                    if (kk < nk) {
-                        const float f = fr[kk];
-                        S[kk] = fmaf(f, S[kk], (1.0f - f) * v);
-                        acc = fmaf(S[kk], qr[kk], acc);
-                    }
+                for (int k4 = 0; k4 < MAXK / 4; k4++) {
+                    const float4 f = f4[k4], w = w4[k4], q = q4[k4];
+                    S[4 * k4 + 0] = fmaf(f.x, S[4 * k4 + 0], w.x * v);
+                    S[4 * k4 + 1] = fmaf(f.y, S[4 * k4 + 1], w.y * v);
+                    S[4 * k4 + 2] = fmaf(f.z, S[4 * k4 + 2], w.z * v);
+                    S[4 * k4 + 3] = fmaf(f.w, S[4 * k4 + 3], w.w * v);
+                    acc = fmaf(S[4 * k4 + 0], q.x, acc);
+                    acc = fmaf(S[4 * k4 + 1], q.y, acc);
+                    acc = fmaf(S[4 * k4 + 2], q.z, acc);
+                    acc = fmaf(S[4 * k4 + 3], q.w, acc);
                 }
-                part[(c * ks + kg) * dv + col] = acc;
+                part[(c * ks + kg) * cb + col_l] = acc;
             }
         }
         __syncthreads();
-        for (int idx = tid; idx < n * dv; idx += blockDim.x) {
-            const int c = idx / dv, j = idx - c * dv;
+        for (int idx = tid; idx < n * cb; idx += blockDim.x) {
+            const int c = idx / cb, j = idx - c * cb;
             float o = 0.0f;
-            for (int g = 0; g < ks; g++) o += part[(c * ks + g) * dv + j];
-            os[idx] = o;
+            for (int g = 0; g < ks; g++) o += part[(c * ks + g) * cb + j];
+            if (raw_out) {
+                const int jj = blockIdx.z * cb + j;
+                if (jj < dv) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + jj] = o;
+            } else {
+                os[idx] = o;
+            }
         }
         __syncthreads();
-        for (int c = warp; c < n; c += n_warps) {
-            float ss = 0.0f;
-            for (int j = lane; j < dv; j += 32) ss = fmaf(os[c * dv + j], os[c * dv + j], ss);
-            ss = ib::warp_sum(ss);
-            const float f = rsqrtf(ss / float(dv) + eps);
-            TOut* o = out + ((t0 + c0 + c) * n_heads + h) * int64_t(dv);
-            for (int j = lane; j < dv; j += 32) o[j] = ib::from_f32<TOut>(os[c * dv + j] * f * norm_w[j]);
+        if (!raw_out) {
+            for (int c = warp; c < n; c += n_warps) {
+                float ss = 0.0f;
+                for (int j = lane; j < dv; j += 32) ss = fmaf(os[c * cb + j], os[c * cb + j], ss);
+                ss = ib::warp_sum(ss);
+                const float f = rsqrtf(ss / float(dv) + eps);
+                TOut* o = out + ((t0 + c0 + c) * n_heads + h) * int64_t(dv);
+                for (int j = lane; j < dv; j += 32) o[j] = ib::from_f32<TOut>(os[c * cb + j] * f * norm_w[j]);
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
     if (write_state) {
 #pragma unroll
-        for (int kk = 0; kk < REC_MAXK; kk++)
+        for (int kk = 0; kk < MAXK; kk++)
             if (kk < nk) S_g[int64_t(k0 + kk) * dv + col] = S[kk];
     }
 }
@@ -412,37 +478,93 @@ IB_EXPORT int ib_gated_sum(const float* x, const float* gates, int64_t ldg, cons
     return ib::check_launch("ib_gated_sum");
 }
 
-// The largest d * dv of a head's state that ib_gated_recurrence takes (threads of a CTA x rows a thread keeps).
-IB_EXPORT int64_t ib_gated_recurrence_max_state() { return int64_t(REC_THREADS) * REC_MAXK; }
+// How the rows of a head's state are shared among threads: ks threads per column with kpt rows each. As many threads
+// as a CTA over all columns may have (1024, or 512 where a thread keeps more than 8 rows), so that a thread's share
+// is short; the choice depends on (d, dv) only. Returns false if the head does not fit.
+static bool recurrence_split(int d, int dv, int* ks, int* kpt) {
+    if (d <= 0 || dv <= 0 || dv > 1024) return false;
+    int k = 1024 / dv;
+    k = k > d ? d : k;
+    int per = (d + k - 1) / k;
+    if (per > 8) {
+        k = 512 / dv;
+        if (k < 1) return false;
+        k = k > d ? d : k;
+        per = (d + k - 1) / k;
+        if (per > 32) return false;
+    }
+    k = (d + per - 1) / per;                       // no thread group without rows
+    *ks = k;
+    *kpt = per;
+    return true;
+}
 
-IB_EXPORT int ib_gated_recurrence(const float* proj, int64_t ld, int q_col, int f_col, int v_col, const float* lower,
+// 1 if a head's state of d x dv fits the recurrence kernel's registers, else 0.
+IB_EXPORT int ib_gated_recurrence_fits(int d, int dv) {
+    int ks, kpt;
+    return recurrence_split(d, dv, &ks, &kpt) ? 1 : 0;
+}
+
+template <typename TOut, int MAXK>
+static int launch_recurrence(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* proj, int64_t ld,
+                             int q_col, int f_col, int v_col, const float* lower, const float* norm_w, float eps,
+                             float* state, const int* seg_start, const int* seg_slot, TOut* out, float* raw_out,
+                             int n_heads, int d, int dv, int ks, int kpt, int cb, int chunk, int activated, int write_state) {
+    IB_LAUNCH((gated_recurrence_kernel<TOut, MAXK>), grid, threads, smem, proj, ld, q_col, f_col, v_col, lower, norm_w, eps,
+              state, seg_start, seg_slot, out, raw_out, n_heads, d, dv, ks, kpt, cb, chunk, activated, write_state);
+    return ib::check_launch("ib_gated_recurrence");
+}
+
+// `spread` 0: one CTA per (segment, head), one launch. `spread` 1 (prompt portions): gates in place first, then CTAs
+// per column block that write the bare o into `scratch` (float [tokens, heads * dv]), then the heads' norm.
+// proj is overwritten by the gates in that case. sm_count sizes the column blocks.
+IB_EXPORT int ib_gated_recurrence(float* proj, int64_t ld, int q_col, int f_col, int v_col, const float* lower,
                                   const float* norm_w, float eps, float* state, const int* seg_start,
                                   const int* seg_slot, void* out, int n_segments, int n_heads, int d, int dv,
-                                  int write_state, int out_dtype, cudaStream_t stream) {
+                                  int write_state, int out_dtype, cudaStream_t stream, int spread, float* scratch,
+                                  int64_t n_tokens, int sm_count) {
     if (n_segments <= 0) return IB_OK;
-    if (d <= 0 || dv <= 0 || n_heads <= 0 || dv > REC_THREADS) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: bad sizes %d x %d", d, dv);
-    if (n_heads > 65535) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: too many heads");
-    // rows of the state are shared among `ks` threads per column: as few as keep a thread's share within REC_MAXK
-    // rows, but enough to fill a CTA of 256 threads where the head allows. The choice depends on (d, dv) only.
-    int ks = (d + REC_MAXK - 1) / REC_MAXK;
-    while (ks * dv < 256 && ks < d && (ks + 1) * dv <= REC_THREADS) ks++;
-    if (int64_t(ks) * dv > REC_THREADS)
-        return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: a head's state of %d x %d is beyond %d rows x %d threads", d, dv, REC_MAXK, REC_THREADS);
-    const int kpt = (d + ks - 1) / ks;
-    const int threads = (ks * dv + 31) / 32 * 32;
-    const int per_token = 2 * d + dv + ks * dv + dv;
+    int ks, kpt;
+    if (n_heads <= 0 || n_heads > 65535 || !recurrence_split(d, dv, &ks, &kpt))
+        return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: %d heads with a state of %d x %d do not fit", n_heads, d, dv);
+    if (out_dtype != IB_F32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: unknown output dtype %d", out_dtype);
+    const int maxk = kpt <= 8 ? 8 : 32;
+    int cb = dv;
+    if (spread) {
+        if (!scratch || n_tokens <= 0) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: the spread form needs scratch rows");
+        // column blocks: enough CTAs for about two per SM, at least 4 columns and 64 threads each
+        const int units = n_segments * n_heads;
+        cb = dv;
+        while (cb > 4 && ks * (cb / 2) >= 64 && units * ((dv + cb - 1) / cb) < 2 * (sm_count > 0 ? sm_count : 148)) cb = (cb + 1) / 2;
+        IB_LAUNCH(recurrence_gates_kernel, blocks_for(n_tokens * n_heads * d, 256), 256, 0, proj, ld, q_col, f_col, lower, n_tokens, n_heads * d);
+    }
+    const int blocks_z = (dv + cb - 1) / cb;
+    const int threads = (ks * cb + 31) / 32 * 32;
+    const int per_token = 3 * ks * maxk + cb + ks * cb + cb;
     int chunk = 11264 / per_token;                           // 44 KB of staging at most
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
     const size_t smem = size_t(chunk) * per_token * sizeof(float);
     if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: a token of %d floats does not fit the staging area", per_token);
-    const dim3 grid{unsigned(n_segments), unsigned(n_heads), 1u};
-    if (out_dtype == IB_F32)
-        IB_LAUNCH(gated_recurrence_kernel<float>, grid, threads, smem, proj, ld, q_col, f_col, v_col, lower, norm_w, eps, state,
-                  seg_start, seg_slot, (float*)out, n_heads, d, dv, ks, kpt, chunk, write_state);
-    else if (out_dtype == IB_BF16)
-        IB_LAUNCH(gated_recurrence_kernel<bf16>, grid, threads, smem, proj, ld, q_col, f_col, v_col, lower, norm_w, eps, state,
-                  seg_start, seg_slot, (bf16*)out, n_heads, d, dv, ks, kpt, chunk, write_state);
-    else
-        return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: unknown output dtype %d", out_dtype);
-    return ib::check_launch("ib_gated_recurrence");
+    const dim3 grid{unsigned(n_segments), unsigned(n_heads), unsigned(blocks_z)};
+    float* raw = spread ? scratch : nullptr;
+    int rc;
+#define IB_REC(TOUT, MK)                                                                                                 \
+    rc = launch_recurrence<TOUT, MK>(grid, threads, smem, stream, proj, ld, q_col, f_col, v_col, lower, norm_w, eps, state, \
+                                     seg_start, seg_slot, (TOUT*)out, raw, n_heads, d, dv, ks, kpt, cb, chunk, spread, write_state)
+    if (out_dtype == IB_F32) {
+        if (maxk == 8) IB_REC(float, 8); else IB_REC(float, 32);
+    } else {
+        if (maxk == 8) IB_REC(bf16, 8); else IB_REC(bf16, 32);
+    }
+#undef IB_REC
+    if (rc) return rc;
+    if (spread) {
+        const int64_t rows = n_tokens * n_heads;
+        if (out_dtype == IB_F32)
+            IB_LAUNCH(head_norm_kernel<float>, blocks_for(rows, 8), 256, 0, (const float*)scratch, norm_w, eps, (float*)out, rows, dv);
+        else
+            IB_LAUNCH(head_norm_kernel<bf16>, blocks_for(rows, 8), 256, 0, (const float*)scratch, norm_w, eps, (bf16*)out, rows, dv);
+        return ib::check_launch("ib_gated_recurrence");
+    }
+    return IB_OK;
 }

@@ -392,19 +392,25 @@ def gated_sum(x: torch.Tensor, gates: Optional[torch.Tensor], p: torch.Tensor, a
     return x
 
 
-def gated_recurrence_max_state() -> int:
-    f = _fn("seq", "ib_gated_recurrence_max_state", [], restype=c_int64)
-    return int(f())
+def gated_recurrence_fits(dim: int, v_dim: int) -> bool:
+    """True if a head's state of dim x v_dim fits the recurrence kernel's registers."""
+    return bool(_fn("seq", "ib_gated_recurrence_fits", [c_int, c_int])(int(dim), int(v_dim)))
+
+
+# Segments of more tokens than this go through the form of the recurrence that spreads a head's columns over CTAs.
+RECURRENCE_SPREAD_FROM = 8
 
 
 def gated_recurrence(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, lower: torch.Tensor,
                      norm_weight: torch.Tensor, eps: float, state: torch.Tensor, seg_start: torch.Tensor,
                      seg_slot: torch.Tensor, n_heads: int, dim: int, v_dim: int, out_dtype: torch.dtype,
-                     write_state: bool = True) -> torch.Tensor:
+                     write_state: bool = True, max_len: int = 1) -> torch.Tensor:
     """The gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q per head, over the tokens of every
     segment in order, from and into ``state`` float32 [slots, heads, dim, v_dim]; f = lower + (1 - lower) *
     sigmoid(proj[:, f_col:]), q = silu(proj[:, q_col:]), v = proj[:, v_col:] (proj float32 [T, ld]). Each head's o is
-    divided by its root mean square and multiplied by ``norm_weight`` [v_dim]. Returns [T, heads * v_dim]."""
+    divided by its root mean square and multiplied by ``norm_weight`` [v_dim]. Returns [T, heads * v_dim].
+    ``max_len`` is the longest segment (known on the host): from RECURRENCE_SPREAD_FROM tokens on, the columns of a
+    head are spread over several CTAs and ``proj`` is overwritten with the gates; the results have the same bits."""
     _check(proj, "proj", torch.float32)
     T, ld = proj.shape
     _check(lower, "lower", torch.float32, (n_heads * dim,))
@@ -417,9 +423,12 @@ def gated_recurrence(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, low
     S = seg_slot.numel()
     _check(seg_start, "seg_start", torch.int32, (S + 1,))
     out = torch.empty((T, n_heads * v_dim), dtype=out_dtype, device=proj.device)
+    spread = int(max_len) >= RECURRENCE_SPREAD_FROM
+    scratch = torch.empty((T, n_heads * v_dim), dtype=torch.float32, device=proj.device) if spread else None
+    sm_count = torch.cuda.get_device_properties(proj.device).multi_processor_count if spread else 0
     f = _fn("seq", "ib_gated_recurrence", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 4 +
-            [c_int] * 6 + [c_void_p])
+            [c_int] * 6 + [c_void_p, c_int, c_void_p, c_int64, c_int])
     _call(f, proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col), lower.data_ptr(), norm_weight.data_ptr(), float(eps),
           state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, dim, v_dim,
-          int(write_state), dtype_code(out_dtype), _stream())
+          int(write_state), dtype_code(out_dtype), _stream(), int(spread), _ptr(scratch), T, sm_count)
     return out

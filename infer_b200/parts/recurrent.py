@@ -44,9 +44,8 @@ class GatedLinearRecurrence(Mixer):
         self.eps = float(spec["norm_eps"])
         if min(self.hidden, self.n_heads, self.dim, self.v_dim) <= 0 or self.eps <= 0:
             raise ValueError("gated_linear_recurrence needs positive sizes and eps")
-        if self.dim * self.v_dim > ops.gated_recurrence_max_state():
-            raise ValueError(f"a head's state of {self.dim} x {self.v_dim} is beyond what the recurrence kernel keeps "
-                             f"in registers ({ops.gated_recurrence_max_state()} values)")
+        if not ops.gated_recurrence_fits(self.dim, self.v_dim):
+            raise ValueError(f"a head's state of {self.dim} x {self.v_dim} is beyond what the recurrence kernel keeps in registers")
         self.proj: Optional[Linear] = None
         self.o: Optional[Linear] = None
         self.lower = self.norm_w = None
@@ -88,7 +87,7 @@ class GatedLinearRecurrence(Mixer):
         nq = self.n_heads * self.dim
         proj = self.proj(x, out_dtype=torch.float32)                  # [T, q | f | v], bias of f added
         o = ops.gated_recurrence(proj, 0, nq, 2 * nq, self.lower, self.norm_w, self.eps, cache["S"], step.seg_start,
-                                 step.seg_slot, self.n_heads, self.dim, self.v_dim, self.rt.dtype, write_cache)
+                                 step.seg_slot, self.n_heads, self.dim, self.v_dim, self.rt.dtype, write_cache, step.max_q_len)
         if residual is None:
             return self.o(o, out_dtype=torch.float32)
         return self.o(o, residual=residual)

@@ -121,8 +121,9 @@ def test_gated_recurrence_over_steps_and_slots(out_dtype, sizes):
     for lens in ([1, 1], [2, 3], [30, 1], [1, 2], [16, 12]):
         step = _Step(lens, [at[1], at[3]], [1, 3])
         rows = torch.cat([proj[1][at[1]:at[1] + lens[0]], proj[3][at[3]:at[3] + lens[1]]]).to(DEV).contiguous()
+        # the longest segment chooses the form: one CTA per head, or a head's columns spread over CTAs
         o = ops.gated_recurrence(rows, 2, 2 + Hh * d, 4 + 2 * Hh * d, lower.to(DEV), nw.to(DEV), eps, state, step.seg_start,
-                                 step.seg_slot, Hh, d, dv, out_dtype).double().cpu()
+                                 step.seg_slot, Hh, d, dv, out_dtype, True, max(lens)).double().cpu()
         want = torch.cat([ref[1][0][at[1]:at[1] + lens[0]], ref[3][0][at[3]:at[3] + lens[1]]])
         assert torch.allclose(o, want, **(dict(rtol=2e-2, atol=2e-2) if out_dtype == torch.bfloat16 else dict(rtol=2e-4, atol=2e-5)))
         at[1] += lens[0]
@@ -136,6 +137,25 @@ def test_gated_recurrence_over_steps_and_slots(out_dtype, sizes):
     ops.gated_recurrence(proj[1][:3].to(DEV).contiguous(), 2, 2 + Hh * d, 4 + 2 * Hh * d, lower.to(DEV), nw.to(DEV), eps, state,
                          step.seg_start, step.seg_slot, Hh, d, dv, out_dtype, write_state=False)
     assert torch.equal(state, before)
+
+
+@pytest.mark.parametrize("sizes", [(2, 16, 48), (1, 40, 20), (2, 64, 128), (1, 128, 128)])
+def test_both_forms_of_the_recurrence_give_the_same_bits(sizes):
+    Hh, d, dv = sizes
+    g = torch.Generator().manual_seed(11)
+    lens = [37, 1, 9]
+    step = _Step(lens, [0, 5, 3], [2, 0, 1])
+    ld = 2 * Hh * d + Hh * dv
+    proj = torch.randn(sum(lens), ld, generator=g).to(DEV)
+    lower, nw = (torch.rand(Hh * d, generator=g) * 0.9).to(DEV), (1.0 + 0.1 * torch.randn(dv, generator=g)).to(DEV)
+    state0 = torch.randn(3, Hh, d, dv, generator=g).to(DEV)
+    outs, states = [], []
+    for max_len in (1, max(lens)):
+        st = state0.clone()
+        outs.append(ops.gated_recurrence(proj.clone(), 0, Hh * d, 2 * Hh * d, lower, nw, 1e-6, st, step.seg_start, step.seg_slot,
+                                         Hh, d, dv, torch.float32, True, max_len))
+        states.append(st)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
