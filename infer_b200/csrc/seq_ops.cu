@@ -96,8 +96,8 @@ constexpr int PREP_PAIRS = 4;           // heads of up to 64 * PREP_PAIRS channe
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, const float* __restrict__ filt_w, int taps,
-                   const T* __restrict__ tails, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, int col_base, int inline_tail,
+                   const float* __restrict__ filt_w, int taps, T* tails, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                    int n_rot, int norm_v, float eps, const int* __restrict__ positions,
                    const int* __restrict__ token_seg, const int* __restrict__ seg_start,
                    const int* __restrict__ seg_slot, const int* __restrict__ block_table, int64_t max_blocks,
@@ -128,13 +128,23 @@ qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, const float* __restri
         const int p = lane + 32 * r;
         a[r] = b[r] = 0.0f;
         if (2 * p < width) {
-            const int c = col0 + 2 * p;
+            const int c = col0 + 2 * p;                          // channel; its column in the rows is col_base + c
             if (filt) {
-                a[r] = filtered(rows, ld, t, i_local, c, filt_w + int64_t(c) * taps, taps, tail + c, channels);
-                b[r] = filtered(rows, ld, t, i_local, c + 1, filt_w + int64_t(c + 1) * taps, taps, tail + c + 1, channels);
+                a[r] = filtered(rows, ld, t, i_local, col_base + c, filt_w + int64_t(c) * taps, taps, tail + c, channels);
+                b[r] = filtered(rows, ld, t, i_local, col_base + c + 1, filt_w + int64_t(c + 1) * taps, taps, tail + c + 1, channels);
+                if (inline_tail && taps > 1) {
+                    // one token per request: this lane is the only reader of the two channels' tails; it moves them
+                    T* tw = tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c;
+                    for (int idx = 0; idx + 1 < taps - 1; idx++) {
+                        tw[int64_t(idx) * channels] = tw[int64_t(idx + 1) * channels];
+                        tw[int64_t(idx) * channels + 1] = tw[int64_t(idx + 1) * channels + 1];
+                    }
+                    tw[int64_t(taps - 2) * channels] = rows[t * ld + col_base + c];
+                    tw[int64_t(taps - 2) * channels + 1] = rows[t * ld + col_base + c + 1];
+                }
             } else {
-                a[r] = ib::to_f32(rows[t * ld + c]);
-                b[r] = ib::to_f32(rows[t * ld + c + 1]);
+                a[r] = ib::to_f32(rows[t * ld + col_base + c]);
+                b[r] = ib::to_f32(rows[t * ld + col_base + c + 1]);
             }
             if (kind != 2 && cos_t && 2 * p < n_rot) {
                 const float cs = cos_t[int64_t(pos) * (n_rot / 2) + p], sn = sin_t[int64_t(pos) * (n_rot / 2) + p];
@@ -195,12 +205,14 @@ __global__ void head_gate_kernel(T* __restrict__ ctx, const T* __restrict__ rows
 
 // ------------------------------------------------------------------------------------------------
 // tanh-GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// Input: columns [col0, col0 + width) of rows with leading dimension ld; output contiguous [tokens, width].
 template <typename T>
-__global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n) {
+__global__ void gelu_tanh_kernel(const T* __restrict__ x, int64_t ld, int col0, int64_t width, T* __restrict__ out, int64_t n) {
     ib::pdl_wait();
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float z = ib::to_f32(x[i]);
+    const int64_t t = i / width;
+    const float z = ib::to_f32(x[t * ld + col0 + (i - t * width)]);
     out[i] = ib::from_f32<T>(0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
 }
 
@@ -271,26 +283,59 @@ __global__ void head_norm_kernel(const float* __restrict__ o, const float* __res
     for (int j = lane; j < dv; j += 32) out[r * dv + j] = ib::from_f32<TOut>(x[j] * f * w[j]);
 }
 
+// One chunk of staged tokens through a thread's share of the state: the arithmetic of both forms of the kernel.
+// qs, fs: [token][ks][MAXK] (stride kstride); vs: [token][cb]; part: [token][ks][cb].
+template <int MAXK>
+__device__ __forceinline__ void recurrence_chunk(float (&S)[MAXK], const float* qs, const float* fs, const float* vs,
+                                                 float* part, int n, int kstride, int kg, int ks, int cb, int col_l) {
+#pragma unroll 2
+    for (int c = 0; c < n; c++) {
+        const float v = vs[c * cb + col_l];
+        const float4* f4 = reinterpret_cast<const float4*>(fs + c * kstride + kg * MAXK);
+        const float4* q4 = reinterpret_cast<const float4*>(qs + c * kstride + kg * MAXK);
+        float acc = 0.0f;
+#pragma unroll
+        for (int k4 = 0; k4 < MAXK / 4; k4++) {
+            const float4 f = f4[k4], q = q4[k4];
+            S[4 * k4 + 0] = fmaf(f.x, S[4 * k4 + 0], (1.0f - f.x) * v);
+            S[4 * k4 + 1] = fmaf(f.y, S[4 * k4 + 1], (1.0f - f.y) * v);
+            S[4 * k4 + 2] = fmaf(f.z, S[4 * k4 + 2], (1.0f - f.z) * v);
+            S[4 * k4 + 3] = fmaf(f.w, S[4 * k4 + 3], (1.0f - f.w) * v);
+            acc = fmaf(S[4 * k4 + 0], q.x, acc);
+            acc = fmaf(S[4 * k4 + 1], q.y, acc);
+            acc = fmaf(S[4 * k4 + 2], q.z, acc);
+            acc = fmaf(S[4 * k4 + 3], q.w, acc);
+        }
+        part[(c * ks + kg) * cb + col_l] = acc;
+    }
+}
+
+__device__ __forceinline__ void copy16_async(float* smem_dst, const float* gmem_src) {
+    const uint32_t d = uint32_t(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+
 template <typename TOut, int MAXK>
 __global__ void __launch_bounds__(MAXK > 8 ? 512 : 1024)
 gated_recurrence_kernel(const float* __restrict__ proj, int64_t ld, int q_col, int f_col, int v_col,
                         const float* __restrict__ lower, const float* __restrict__ norm_w, float eps,
                         float* __restrict__ state, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                         TOut* __restrict__ out, float* __restrict__ raw_out, int n_heads, int d, int dv, int ks, int kpt,
-                        int cb, int chunk, int activated, int write_state) {
+                        int cb, int chunk, int activated, int write_state, int pipelined) {
     ib::pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    const int kstride = ks * MAXK;               // staged rows: [kg][MAXK], zero beyond the head's d rows
-    float* qs = sm;                              // [chunk][ks][MAXK]
-    float* fs = qs + chunk * kstride;
-    float* ws = fs + chunk * kstride;            // 1 - f
-    float* vs = ws + chunk * kstride;            // [chunk][cb]
-    float* part = vs + chunk * cb;               // [chunk][ks][cb]
-    float* os = part + chunk * ks * cb;          // [chunk][cb]
+    const int kstride = ks * MAXK;               // staged rows: [kg][MAXK]; a padded row f = 0 keeps a state row at zero
+    const int n_buf = pipelined ? 2 : 1;
+    float* qs = sm;                              // [n_buf][chunk][ks][MAXK]
+    float* fs = qs + n_buf * chunk * kstride;
+    float* vs = fs + n_buf * chunk * kstride;    // [n_buf][chunk][cb]
+    float* part = vs + n_buf * chunk * cb;       // [chunk][ks][cb]
+    float* os = part + chunk * ks * cb;          // [chunk][cb] (the form with the norm inside only)
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
     const int col_l = tid % cb, kg = tid / cb;
-    const int col = blockIdx.z * cb + col_l;
+    const int col0 = blockIdx.z * cb;
+    const int col = col0 + col_l;
     const bool active = kg < ks && col < dv;
     const int k0 = kg * kpt;
     const int nk = active ? max(0, min(kpt, d - k0)) : 0;
@@ -301,77 +346,96 @@ gated_recurrence_kernel(const float* __restrict__ proj, int64_t ld, int q_col, i
 #pragma unroll
     for (int kk = 0; kk < MAXK; kk++) S[kk] = kk < nk ? S_g[int64_t(k0 + kk) * dv + col] : 0.0f;
 
-    for (int c0 = 0; c0 < len; c0 += chunk) {
-        const int n = min(chunk, len - c0);
-        for (int idx = tid; idx < n * kstride; idx += blockDim.x) {
-            const int c = idx / kstride, r = idx - c * kstride;
-            const int g = r / MAXK, kk = r - g * MAXK;
-            const int k = g * kpt + kk;
-            float q = 0.0f, f = 0.0f, w = 0.0f;
-            if (kk < kpt && k < d) {
+    if (pipelined) {
+        // Prompt portions, gates already applied, d = ks * MAXK, every column offset a multiple of four floats: the
+        // rows are copied as they lie, 16 bytes per asynchronous copy, one chunk ahead of the one being computed.
+        const int q4 = d / 4, v4 = cb / 4;
+        auto request = [&](int c0, int b) {
+            const int n = min(chunk, len - c0);
+            for (int idx = tid; idx < n * q4; idx += blockDim.x) {
+                const int c = idx / q4, j = (idx - c * q4) * 4;
                 const float* row = proj + (t0 + c0 + c) * ld;
-                q = row[q_col + h * d + k];
-                f = row[f_col + h * d + k];
-                if (!activated) {
-                    q = silu_value(q);
-                    f = forget_value(lower[h * d + k], f);
-                }
-                w = 1.0f - f;
+                copy16_async(qs + (b * chunk + c) * kstride + j, row + q_col + h * d + j);
+                copy16_async(fs + (b * chunk + c) * kstride + j, row + f_col + h * d + j);
             }
-            qs[idx] = q;
-            fs[idx] = f;
-            ws[idx] = w;
-        }
-        for (int idx = tid; idx < n * cb; idx += blockDim.x) {
-            const int c = idx / cb, j = blockIdx.z * cb + (idx - c * cb);
-            vs[idx] = j < dv ? proj[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
-        }
-        __syncthreads();
-        if (active) {
-            for (int c = 0; c < n; c++) {
-                const float v = vs[c * cb + col_l];
-                const float4* f4 = reinterpret_cast<const float4*>(fs + c * kstride + kg * MAXK);
-                const float4* w4 = reinterpret_cast<const float4*>(ws + c * kstride + kg * MAXK);
-                const float4* q4 = reinterpret_cast<const float4*>(qs + c * kstride + kg * MAXK);
-                float acc = 0.0f;
-#pragma unroll
-                for (int k4 = 0; k4 < MAXK / 4; k4++) {
-                    const float4 f = f4[k4], w = w4[k4], q = q4[k4];
-                    S[4 * k4 + 0] = fmaf(f.x, S[4 * k4 + 0], w.x * v);
-                    S[4 * k4 + 1] = fmaf(f.y, S[4 * k4 + 1], w.y * v);
-                    S[4 * k4 + 2] = fmaf(f.z, S[4 * k4 + 2], w.z * v);
-                    S[4 * k4 + 3] = fmaf(f.w, S[4 * k4 + 3], w.w * v);
-                    acc = fmaf(S[4 * k4 + 0], q.x, acc);
-                    acc = fmaf(S[4 * k4 + 1], q.y, acc);
-                    acc = fmaf(S[4 * k4 + 2], q.z, acc);
-                    acc = fmaf(S[4 * k4 + 3], q.w, acc);
-                }
-                part[(c * ks + kg) * cb + col_l] = acc;
+            for (int idx = tid; idx < n * v4; idx += blockDim.x) {
+                const int c = idx / v4, j = (idx - c * v4) * 4;
+                if (col0 + j < dv)
+                    copy16_async(vs + (b * chunk + c) * cb + j, proj + (t0 + c0 + c) * ld + v_col + h * dv + col0 + j);
             }
-        }
-        __syncthreads();
-        for (int idx = tid; idx < n * cb; idx += blockDim.x) {
-            const int c = idx / cb, j = idx - c * cb;
-            float o = 0.0f;
-            for (int g = 0; g < ks; g++) o += part[(c * ks + g) * cb + j];
-            if (raw_out) {
-                const int jj = blockIdx.z * cb + j;
-                if (jj < dv) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + jj] = o;
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        request(0, 0);
+        int b = 0;
+        for (int c0 = 0; c0 < len; c0 += chunk, b ^= 1) {
+            const int n = min(chunk, len - c0);
+            if (c0 + chunk < len) {
+                request(c0 + chunk, b ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
             } else {
-                os[idx] = o;
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();                     // the chunk has arrived; the last chunk's sums have been read
+            if (active)
+                recurrence_chunk<MAXK>(S, qs + b * chunk * kstride, fs + b * chunk * kstride, vs + b * chunk * cb, part, n,
+                                       kstride, kg, ks, cb, col_l);
+            __syncthreads();
+            for (int idx = tid; idx < n * cb; idx += blockDim.x) {
+                const int c = idx / cb, j = idx - c * cb;
+                float o = 0.0f;
+                for (int g = 0; g < ks; g++) o += part[(c * ks + g) * cb + j];
+                if (col0 + j < dv) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + col0 + j] = o;
             }
         }
-        __syncthreads();
-        if (!raw_out) {
-            for (int c = warp; c < n; c += n_warps) {
-                float ss = 0.0f;
-                for (int j = lane; j < dv; j += 32) ss = fmaf(os[c * cb + j], os[c * cb + j], ss);
-                ss = ib::warp_sum(ss);
-                const float f = rsqrtf(ss / float(dv) + eps);
-                TOut* o = out + ((t0 + c0 + c) * n_heads + h) * int64_t(dv);
-                for (int j = lane; j < dv; j += 32) o[j] = ib::from_f32<TOut>(os[c * cb + j] * f * norm_w[j]);
+    } else {
+        for (int c0 = 0; c0 < len; c0 += chunk) {
+            const int n = min(chunk, len - c0);
+            for (int idx = tid; idx < n * kstride; idx += blockDim.x) {
+                const int c = idx / kstride, r = idx - c * kstride;
+                const int g = r / MAXK, kk = r - g * MAXK;
+                const int k = g * kpt + kk;
+                float q = 0.0f, f = 0.0f;
+                if (kk < kpt && k < d) {
+                    const float* row = proj + (t0 + c0 + c) * ld;
+                    q = row[q_col + h * d + k];
+                    f = row[f_col + h * d + k];
+                    if (!activated) {
+                        q = silu_value(q);
+                        f = forget_value(lower[h * d + k], f);
+                    }
+                }
+                qs[idx] = q;
+                fs[idx] = f;
+            }
+            for (int idx = tid; idx < n * cb; idx += blockDim.x) {
+                const int c = idx / cb, j = col0 + (idx - c * cb);
+                vs[idx] = j < dv ? proj[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
             }
             __syncthreads();
+            if (active) recurrence_chunk<MAXK>(S, qs, fs, vs, part, n, kstride, kg, ks, cb, col_l);
+            __syncthreads();
+            for (int idx = tid; idx < n * cb; idx += blockDim.x) {
+                const int c = idx / cb, j = idx - c * cb;
+                float o = 0.0f;
+                for (int g = 0; g < ks; g++) o += part[(c * ks + g) * cb + j];
+                if (raw_out) {
+                    if (col0 + j < dv) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + col0 + j] = o;
+                } else {
+                    os[idx] = o;
+                }
+            }
+            __syncthreads();
+            if (!raw_out) {
+                for (int c = warp; c < n; c += n_warps) {
+                    float ss = 0.0f;
+                    for (int j = lane; j < dv; j += 32) ss = fmaf(os[c * cb + j], os[c * cb + j], ss);
+                    ss = ib::warp_sum(ss);
+                    const float f = rsqrtf(ss / float(dv) + eps);
+                    TOut* o = out + ((t0 + c0 + c) * n_heads + h) * int64_t(dv);
+                    for (int j = lane; j < dv; j += 32) o[j] = ib::from_f32<TOut>(os[c * cb + j] * f * norm_w[j]);
+                }
+                __syncthreads();
+            }
         }
     }
     if (write_state) {
@@ -420,7 +484,7 @@ IB_EXPORT int ib_filter_tail(const void* rows, int64_t ld, int col0, int channel
 // The widest head (keys or values) that ib_qkv_prepare takes.
 IB_EXPORT int ib_qkv_prepare_max_head_dim() { return 64 * PREP_PAIRS; }
 
-IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, const float* filt_w, int taps, const void* tails,
+IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, int col_base, int inline_tail, const float* filt_w, int taps, void* tails,
                              const float* cos_t, const float* sin_t, int n_rot, int norm_v, float eps,
                              const int* positions, const int* token_seg, const int* seg_start, const int* seg_slot,
                              const int* block_table, int64_t max_blocks, void* q_out, void* k_cache, void* v_cache,
@@ -434,11 +498,11 @@ IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, const float* filt_w, 
     if (n_heads <= 0 || n_kv <= 0 || page_size <= 0) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: bad sizes");
     const int64_t warps = n_tokens * (n_heads + 2 * n_kv);
     if (dtype == IB_F32)
-        IB_LAUNCH(qkv_prepare_kernel<float>, blocks_for(warps, 4), 128, 0, (const float*)rows, ld, filt_w, taps, (const float*)tails, cos_t, sin_t,
+        IB_LAUNCH(qkv_prepare_kernel<float>, blocks_for(warps, 4), 128, 0, (const float*)rows, ld, col_base, inline_tail, filt_w, taps, (float*)tails, cos_t, sin_t,
                   n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (float*)q_out,
                   (float*)k_cache, (float*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
     else if (dtype == IB_BF16)
-        IB_LAUNCH(qkv_prepare_kernel<bf16>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, filt_w, taps, (const bf16*)tails, cos_t, sin_t,
+        IB_LAUNCH(qkv_prepare_kernel<bf16>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
                   n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
                   (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
     else
@@ -459,12 +523,14 @@ IB_EXPORT int ib_head_gate(void* ctx, const void* rows, int64_t ld, int gate_col
     return ib::check_launch("ib_head_gate");
 }
 
-IB_EXPORT int ib_gelu_tanh(const void* x, void* out, int64_t n, int dtype, cudaStream_t stream) {
+IB_EXPORT int ib_gelu_tanh(const void* x, int64_t ld, int col0, int64_t width, void* out, int64_t n_tokens, int dtype,
+                           cudaStream_t stream) {
+    const int64_t n = n_tokens * width;
     if (n <= 0) return IB_OK;
     if (dtype == IB_F32)
-        IB_LAUNCH(gelu_tanh_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)x, (float*)out, n);
+        IB_LAUNCH(gelu_tanh_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)x, ld, col0, width, (float*)out, n);
     else if (dtype == IB_BF16)
-        IB_LAUNCH(gelu_tanh_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)x, (bf16*)out, n);
+        IB_LAUNCH(gelu_tanh_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)x, ld, col0, width, (bf16*)out, n);
     else
         return ib::fail(IB_ERR_ARG, "ib_gelu_tanh: unknown dtype %d", dtype);
     return ib::check_launch("ib_gelu_tanh");
@@ -509,9 +575,10 @@ template <typename TOut, int MAXK>
 static int launch_recurrence(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* proj, int64_t ld,
                              int q_col, int f_col, int v_col, const float* lower, const float* norm_w, float eps,
                              float* state, const int* seg_start, const int* seg_slot, TOut* out, float* raw_out,
-                             int n_heads, int d, int dv, int ks, int kpt, int cb, int chunk, int activated, int write_state) {
+                             int n_heads, int d, int dv, int ks, int kpt, int cb, int chunk, int activated, int write_state,
+                             int pipelined) {
     IB_LAUNCH((gated_recurrence_kernel<TOut, MAXK>), grid, threads, smem, proj, ld, q_col, f_col, v_col, lower, norm_w, eps,
-              state, seg_start, seg_slot, out, raw_out, n_heads, d, dv, ks, kpt, cb, chunk, activated, write_state);
+              state, seg_start, seg_slot, out, raw_out, n_heads, d, dv, ks, kpt, cb, chunk, activated, write_state, pipelined);
     return ib::check_launch("ib_gated_recurrence");
 }
 
@@ -530,17 +597,21 @@ IB_EXPORT int ib_gated_recurrence(float* proj, int64_t ld, int q_col, int f_col,
     if (out_dtype != IB_F32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: unknown output dtype %d", out_dtype);
     const int maxk = kpt <= 8 ? 8 : 32;
     int cb = dv;
+    int pipelined = 0;
     if (spread) {
         if (!scratch || n_tokens <= 0) return ib::fail(IB_ERR_ARG, "ib_gated_recurrence: the spread form needs scratch rows");
-        // column blocks: enough CTAs for about two per SM, at least 4 columns and 64 threads each
-        const int units = n_segments * n_heads;
-        cb = dv;
-        while (cb > 4 && ks * (cb / 2) >= 64 && units * ((dv + cb - 1) / cb) < 2 * (sm_count > 0 ? sm_count : 148)) cb = (cb + 1) / 2;
+        // Column blocks: the chain over a segment's tokens is the critical path, so a head's columns are spread over
+        // CTAs of at least 128 threads (a warp per scheduler) until there is about one CTA per SM.
+        const int units = n_segments * n_heads, sms = sm_count > 0 ? sm_count : 148;
+        while (cb % 8 == 0 && ks * (cb / 2) >= 128 && units * ((dv + cb / 2 - 1) / (cb / 2)) <= sms) cb /= 2;
+        pipelined = d == ks * maxk && kpt == maxk && d % 4 == 0 && cb % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 &&
+                    f_col % 4 == 0 && v_col % 4 == 0 && !(uintptr_t(proj) & 15);
         IB_LAUNCH(recurrence_gates_kernel, blocks_for(n_tokens * n_heads * d, 256), 256, 0, proj, ld, q_col, f_col, lower, n_tokens, n_heads * d);
     }
     const int blocks_z = (dv + cb - 1) / cb;
     const int threads = (ks * cb + 31) / 32 * 32;
-    const int per_token = 3 * ks * maxk + cb + ks * cb + cb;
+    const int n_buf = pipelined ? 2 : 1;
+    const int per_token = n_buf * (2 * ks * maxk + cb) + ks * cb + (spread ? 0 : cb);
     int chunk = 11264 / per_token;                           // 44 KB of staging at most
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
     const size_t smem = size_t(chunk) * per_token * sizeof(float);
@@ -550,7 +621,7 @@ IB_EXPORT int ib_gated_recurrence(float* proj, int64_t ld, int q_col, int f_col,
     int rc;
 #define IB_REC(TOUT, MK)                                                                                                 \
     rc = launch_recurrence<TOUT, MK>(grid, threads, smem, stream, proj, ld, q_col, f_col, v_col, lower, norm_w, eps, state, \
-                                     seg_start, seg_slot, (TOUT*)out, raw, n_heads, d, dv, ks, kpt, cb, chunk, spread, write_state)
+                                     seg_start, seg_slot, (TOUT*)out, raw, n_heads, d, dv, ks, kpt, cb, chunk, spread, write_state, pipelined)
     if (out_dtype == IB_F32) {
         if (maxk == 8) IB_REC(float, 8); else IB_REC(float, 32);
     } else {

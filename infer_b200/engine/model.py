@@ -88,4 +88,7 @@ class Model:
                         visit(v, depth + 1)
         for p in self.all_parts():
             visit(p)
+        for b in self.blocks:                     # products that a block joined out of its parts' first matrices
+            for joined in getattr(b, "joined", ()):
+                visit(joined[0])
         return total

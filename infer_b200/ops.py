@@ -306,8 +306,10 @@ def qkv_prepare_max_head_dim() -> int:
 def qkv_prepare(rows: torch.Tensor, filt_w: Optional[torch.Tensor], tails: Optional[torch.Tensor],
                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], n_rot: int, norm_v: bool, eps: float,
                 step, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, write_cache: bool = True) -> torch.Tensor:
-    """Projected rows [q | k | v | anything] -> q [T, heads * head_dim] for attention, k and v into their pages.
+                n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, write_cache: bool = True, col0: int = 0,
+                inline_tail: bool = False) -> torch.Tensor:
+    """Projected rows [... | q | k | v | ...] (q at column ``col0``) -> q [T, heads * head_dim] for attention, k and v
+    into their pages. ``inline_tail`` (only for steps of one token per request): the kernel also moves the tails.
     Optional on the way: a short causal filter on every q, k and v channel (``filt_w`` float32 [channels, taps] with
     the requests' ``tails`` [slots, taps - 1, channels]); rotation of adjacent channel pairs of q and k over the
     first ``n_rot`` channels of each head (tables float32 [positions, n_rot / 2]); v divided by its root mean square
@@ -315,8 +317,8 @@ def qkv_prepare(rows: torch.Tensor, filt_w: Optional[torch.Tensor], tails: Optio
     _check(rows, "rows")
     T, ld = rows.shape
     C = (n_heads + n_kv) * head_dim + n_kv * v_head_dim
-    if ld < C:
-        raise KernelError(f"rows of {ld} columns cannot hold q, k and v of {C}")
+    if ld < col0 + C:
+        raise KernelError(f"rows of {ld} columns cannot hold q, k and v of {C} from column {col0}")
     n_pages, ckv, page_size, chd = k_cache.shape
     _check(k_cache, "k_cache", rows.dtype, (n_pages, n_kv, page_size, head_dim))
     _check(v_cache, "v_cache", rows.dtype, (n_pages, n_kv, page_size, v_head_dim))
@@ -339,9 +341,9 @@ def qkv_prepare(rows: torch.Tensor, filt_w: Optional[torch.Tensor], tails: Optio
         n_rot = 0
     _check(block_table, "block_table", torch.int32)
     q = torch.empty((T, n_heads * head_dim), dtype=rows.dtype, device=rows.device)
-    f = _fn("seq", "ib_qkv_prepare", [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float] +
+    f = _fn("seq", "ib_qkv_prepare", [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float] +
             [c_void_p] * 5 + [c_int64] + [c_void_p] * 3 + [c_int64] + [c_int] * 6 + [c_int64, c_int, c_void_p, c_void_p])
-    _call(f, rows.data_ptr(), ld, _ptr(filt_w), taps, _ptr(tails) if taps > 1 else None, _ptr(cos), _ptr(sin),
+    _call(f, rows.data_ptr(), ld, int(col0), int(bool(inline_tail) and taps > 1), _ptr(filt_w), taps, _ptr(tails) if taps > 1 else None, _ptr(cos), _ptr(sin),
           int(n_rot), int(bool(norm_v)), float(eps), step.positions.data_ptr(), step.token_seg.data_ptr(),
           step.seg_start.data_ptr(), step.seg_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T, n_heads, n_kv, head_dim, v_head_dim, page_size,
@@ -362,19 +364,24 @@ def head_gate(ctx: torch.Tensor, rows: torch.Tensor, gate_col: int, n_heads: int
     return ctx
 
 
-def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
-    """0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), element by element."""
+def gelu_tanh(x: torch.Tensor, col0: int = 0, width: Optional[int] = None) -> torch.Tensor:
+    """0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), element by element, of columns [col0, col0 + width) of the rows
+    x [T, ld] (default: all of them); the result is contiguous [T, width]."""
     _check(x, "x")
-    out = torch.empty_like(x)
-    f = _fn("seq", "ib_gelu_tanh", [c_void_p, c_void_p, c_int64, c_int, c_void_p])
-    _call(f, x.data_ptr(), out.data_ptr(), x.numel(), dtype_code(x.dtype), _stream())
+    T, ld = x.shape
+    width = ld - col0 if width is None else int(width)
+    if col0 < 0 or width < 0 or col0 + width > ld:
+        raise KernelError("the activation's columns lie outside the rows")
+    out = torch.empty((T, width), dtype=x.dtype, device=x.device)
+    f = _fn("seq", "ib_gelu_tanh", [c_void_p, c_int64, c_int, c_int64, c_void_p, c_int64, c_int, c_void_p])
+    _call(f, x.data_ptr(), ld, int(col0), width, out.data_ptr(), T, dtype_code(x.dtype), _stream())
     return out
 
 
 def gated_sum(x: torch.Tensor, gates: Optional[torch.Tensor], p: torch.Tensor, a: float = 1.0,
-              q: Optional[torch.Tensor] = None, b: float = 1.0, r: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x + sigmoid(gates[:, :W]) * (a p + b q) + sigmoid(gates[:, W:2W]) * r, float32 [T, W], written over x.
-    q and r may be absent; without gates the terms are added as they are."""
+              q: Optional[torch.Tensor] = None, b: float = 1.0, r: Optional[torch.Tensor] = None, gate_col: int = 0) -> torch.Tensor:
+    """x + sigmoid(gates[:, g:g+W]) * (a p + b q) + sigmoid(gates[:, g+W:g+2W]) * r with g = gate_col, float32 [T, W],
+    written over x. q and r may be absent; without gates the terms are added as they are."""
     _check(x, "x", torch.float32)
     T, W = x.shape
     for name, t in (("p", p), ("q", q), ("r", r)):
@@ -384,11 +391,12 @@ def gated_sum(x: torch.Tensor, gates: Optional[torch.Tensor], p: torch.Tensor, a
     if gates is not None:
         _check(gates, "gates", torch.float32)
         ldg = gates.shape[1]
-        if gates.shape[0] != T or ldg < (2 * W if r is not None else W):
+        if gates.shape[0] != T or ldg < gate_col + (2 * W if r is not None else W):
             raise KernelError(f"gates of shape {tuple(gates.shape)} do not cover the terms")
     f = _fn("seq", "ib_gated_sum", [c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p,
                                     c_int64, c_int64, c_void_p])
-    _call(f, x.data_ptr(), _ptr(gates), ldg, p.data_ptr(), float(a), _ptr(q), float(b), _ptr(r), x.data_ptr(), T, W, _stream())
+    g_ptr = None if gates is None else gates.data_ptr() + 4 * int(gate_col)
+    _call(f, x.data_ptr(), g_ptr, ldg, p.data_ptr(), float(a), _ptr(q), float(b), _ptr(r), x.data_ptr(), T, W, _stream())
     return x
 
 

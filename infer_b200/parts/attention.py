@@ -29,7 +29,7 @@ import torch
 
 from .. import ops
 from ..config.specs import PartSpec
-from .base import CompositeNeed, Mixer, PagedKVNeed, StateNeed, build_part, register_mixer
+from .base import CompositeNeed, Mixer, PagedKVNeed, ProjectedInput, StateNeed, build_part, own_or_projected, register_mixer
 from .linear import Linear
 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -150,10 +150,21 @@ class Attention(Mixer):
             return self.o(ctx, out_dtype=torch.float32)
         return self.o(ctx, residual=residual)
 
+    def input_product(self):
+        """The q/k/v(/gate) product, for a block that joins the products of parts reading the same rows. Only the
+        prepared path reads its rows by (leading dimension, first column)."""
+        return (self.qkv, "compute") if self.prepared else None
+
+    def drop_input_product(self):
+        self.qkv = None
+
     def forward(self, x, step, cache, residual, write_cache=True):
-        qkv = self.qkv(x)                                              # [T, (heads + kv) * head_dim + kv * v_dim (+ gates)]
         if self.prepared:
-            return self._forward_prepared(qkv, step, cache, residual, write_cache)
+            qkv, col0 = own_or_projected(self, x, self.qkv)
+            return self._forward_prepared(qkv, col0, step, cache, residual, write_cache)
+        if isinstance(x, ProjectedInput):
+            x = x.rows_in
+        qkv = self.qkv(x)                                              # [T, (heads + 2 kv) * head_dim]
         table = step.block_tables[cache.group]
         tables = self.position.rotary_tables(self.rt.max_seq_len) if self.position is not None else None
         if self.position is not None and tables is None:
@@ -174,9 +185,10 @@ class Attention(Mixer):
                               self.n_heads, self.n_kv, self.head_dim, write_cache, step.status)
         return self._project_out(self._context(q, cache, table, step), residual)
 
-    def _forward_prepared(self, qkv, step, cache, residual, write_cache):
+    def _forward_prepared(self, qkv, col0, step, cache, residual, write_cache):
         """Filter, pair rotation and value norm in one kernel that also fills the pages; then the filter's tails take
-        the step's last projected rows, attention runs over the pages, and the heads are gated."""
+        the step's last projected rows, attention runs over the pages, and the heads are gated. The part's columns
+        [q | k | v | gates] start at ``col0`` of the rows ``qkv``."""
         pages = cache["pages"] if isinstance(cache, dict) else cache
         tails = cache["tails"]["qkv"] if isinstance(cache, dict) else None
         table = step.block_tables[pages.group]
@@ -185,12 +197,14 @@ class Attention(Mixer):
         if self.position is not None:
             cos, sin = self.position.rotary_tables(self.rt.max_seq_len)
             n_rot = self.position.rotary_dims
+        # with one token per request, the thread that filters a channel is the only reader of its tail and moves it too
+        inline_tail = tails is not None and write_cache and step.max_q_len == 1
         q = ops.qkv_prepare(qkv, self.filter_w, tails, cos, sin, n_rot, self.value_norm_eps is not None,
                             float(self.value_norm_eps or 0.0), step, table, pages.k, pages.v, self.n_heads, self.n_kv,
-                            self.head_dim, self.v_dim, write_cache)
-        if tails is not None and write_cache:
-            ops.filter_tail_update(qkv, 0, tails, step.seg_start, step.seg_slot)
+                            self.head_dim, self.v_dim, write_cache, col0, inline_tail)
+        if tails is not None and write_cache and not inline_tail:
+            ops.filter_tail_update(qkv, col0, tails, step.seg_start, step.seg_slot)
         ctx = self._context(q, pages, table, step)
         if self.head_gate:
-            ops.head_gate(ctx, qkv, self.n_qkv, self.n_heads, self.v_dim)
+            ops.head_gate(ctx, qkv, col0 + self.n_qkv, self.n_heads, self.v_dim)
         return self._project_out(ctx, residual)

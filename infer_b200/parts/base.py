@@ -98,6 +98,37 @@ class DeferredNorm:
         return self._value
 
 
+class ProjectedInput:
+    """What a block hands its parts in place of the normalised rows when it has joined their first matrix products
+    (every one of them reads the same rows) into fewer, larger ones: the results' rows, and for each part that took
+    part, where its own columns start. ``of(part)`` gives that part's (rows, first column) or None; ``rows_in`` are
+    the normalised rows themselves (possibly a DeferredNorm) for parts that did not take part.
+
+    A part takes part by offering ``input_product() -> (Linear, "compute" | "float32")``, its first product and the
+    dtype of the result it wants, and by starting ``forward`` from ``x.of(self)`` when x is a ProjectedInput. The block
+    calls ``drop_input_product()`` on it after joining, so that the matrix lives once."""
+
+    def __init__(self, rows_in):
+        self.rows_in = rows_in
+        self._where = {}
+
+    def place(self, part, rows, col0: int) -> None:
+        self._where[id(part)] = (rows, col0)
+
+    def of(self, part):
+        return self._where.get(id(part))
+
+
+def own_or_projected(part, x, linear, out_dtype=None):
+    """(rows, first column) of a part's first product: its slice of a joined product, or its own ``linear`` on x."""
+    if isinstance(x, ProjectedInput):
+        got = x.of(part)
+        if got is not None:
+            return got
+        x = x.rows_in
+    return linear(x, out_dtype=out_dtype), 0
+
+
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x [rows, size] float32 (the residual stream) -> normalised rows in the compute dtype."""

@@ -9,7 +9,10 @@ that is two mixers side by side hands over both results and their constants, so 
 the residual sum are one float32 kernel."""
 from __future__ import annotations
 
-from .base import Block, DeferredNorm, register_block
+import torch
+
+from .base import Block, DeferredNorm, ProjectedInput, register_block
+from .linear import Linear
 
 
 def normed_input(norm, consumer, h):
@@ -34,6 +37,8 @@ class PreNormBlock(Block):
 
 @register_block("parallel_gated")
 class ParallelGatedBlock(Block):
+    accepts_deferred_norm = True          # (of the joined products: the streaming product normalises inside)
+
     def __init__(self, norm, mixer, gate=None, feed_forward=None):
         parts = {"norm": norm, "mixer": mixer}
         if gate is not None:
@@ -42,14 +47,39 @@ class ParallelGatedBlock(Block):
             parts["feed_forward"] = feed_forward
         super().__init__(**parts)
         self.gate, self.feed_forward = gate, feed_forward
+        # Every sublayer starts with a matrix product on the same rows. Products whose results have the same dtype
+        # are joined into one (two launches per layer instead of four or five, and one read of the rows each).
+        self.joined = []                   # (Linear, out dtype or None for the compute dtype, [(part, first column)])
+        members = []
+        for p in (mixer, gate, feed_forward):
+            members += p.members() if hasattr(p, "members") else ([p] if p is not None else [])
+        offers = [(p, p.input_product()) for p in members if hasattr(p, "input_product")]
+        for kind in ("compute", "float32"):
+            group = [(p, o[0]) for p, o in offers if o is not None and o[1] == kind]
+            if len(group) >= 2:
+                linear, starts = Linear.join(norm.rt, [l for _, l in group])
+                self.joined.append((linear, torch.float32 if kind == "float32" else None, [(p, c) for (p, _), c in zip(group, starts)]))
+                for p, _ in group:
+                    p.drop_input_product()
 
     def forward(self, h, step, cache, write_cache=True):
         from .. import ops
-        n = self.norm.forward(h)
+        n = normed_input(self.norm, self, h)
+        x = ProjectedInput(n)
+        for linear, out_dtype, places in self.joined:
+            rows = linear(n, out_dtype=out_dtype)
+            for part, col0 in places:
+                x.place(part, rows, col0)
+
+        def arg(part):
+            """The joined products' rows for a part that knows them; the normalised rows themselves for any other."""
+            if hasattr(part, "input_product") or hasattr(part, "members"):
+                return x
+            return n.materialize() if isinstance(n, DeferredNorm) else n
         if hasattr(self.mixer, "forward_sides"):
-            p, q, a, b = self.mixer.forward_sides(n, step, cache, write_cache)
+            p, q, a, b = self.mixer.forward_sides(arg(self.mixer), step, cache, write_cache)
         else:
-            p, q, a, b = self.mixer.forward(n, step, cache, None, write_cache), None, 1.0, 1.0
-        r = self.feed_forward.forward(n, None) if self.feed_forward is not None else None
-        gates = self.gate.forward(n) if self.gate is not None else None
-        return ops.gated_sum(h, gates, p, a, q, b, r)
+            p, q, a, b = self.mixer.forward(arg(self.mixer), step, cache, None, write_cache), None, 1.0, 1.0
+        r = self.feed_forward.forward(arg(self.feed_forward), None) if self.feed_forward is not None else None
+        gates, g0 = self.gate.forward(x) if self.gate is not None else (None, 0)
+        return ops.gated_sum(h, gates, p, a, q, b, r, g0)

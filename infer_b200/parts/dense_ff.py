@@ -9,10 +9,10 @@ import torch
 
 from .. import ops
 from ..config.specs import PartSpec
-from .base import FeedForward, register_feed_forward
+from .base import FeedForward, own_or_projected, register_feed_forward
 from .linear import Linear
 
-_ACTIVATIONS = {"gelu_tanh": ops.gelu_tanh}
+_ACTIVATIONS = {"gelu_tanh": ops.gelu_tanh}        # each: (rows, first column, width) -> contiguous [T, width]
 _NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
 
 
@@ -42,8 +42,15 @@ class DenseFeedForward(FeedForward):
         self.up = Linear(self.rt, params[n["up"]])
         self.down = Linear(self.rt, params[n["down"]])
 
+    def input_product(self):
+        return self.up, "compute"
+
+    def drop_input_product(self):
+        self.up = None
+
     def forward(self, x, residual):
-        act = self.activation(self.up(x))
+        rows, c0 = own_or_projected(self, x, self.up)
+        act = self.activation(rows, c0, self.inter)
         if residual is None:
             return self.down(act, out_dtype=torch.float32)
         return self.down(act, residual=residual)

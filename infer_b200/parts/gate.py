@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..config.specs import PartSpec
-from .base import Gate, register_gate
+from .base import Gate, own_or_projected, register_gate
 from .linear import Linear
 
 
@@ -39,5 +39,12 @@ class SigmoidLinearGate(Gate):
         b = torch.cat([params[n + self.bias_suffix].float() for n in self.names])
         self.linear = Linear(self.rt, w, b)
 
+    def input_product(self):
+        return self.linear, "float32"
+
+    def drop_input_product(self):
+        self.linear = None
+
     def forward(self, x):
-        return self.linear(x, out_dtype=torch.float32)
+        """(rows, first column): the gates' logits are columns [first, first + count * hidden) of float32 rows."""
+        return own_or_projected(self, x, self.linear, torch.float32)

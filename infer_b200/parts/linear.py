@@ -31,6 +31,26 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         return self
 
+    @classmethod
+    def join(cls, rt: Runtime, linears, align: int = 8):
+        """One product for several that read the same rows: the matrices stacked (each padded with zero rows to a
+        multiple of ``align``, so that every part's columns start on a 16-byte boundary of the result), biases
+        likewise. Returns (Linear, [first column of each])."""
+        mats, biases, starts, n = [], [], [], 0
+        any_bias = any(l.bias is not None for l in linears)
+        for l in linears:
+            pad = (-l.out_features) % align
+            starts.append(n)
+            mats.append(l.weight)
+            if pad:
+                mats.append(torch.zeros(pad, l.in_features, dtype=l.weight.dtype, device=l.weight.device))
+            if any_bias:
+                biases.append(l.bias if l.bias is not None else torch.zeros(l.out_features, dtype=torch.float32, device=l.weight.device))
+                if pad:
+                    biases.append(torch.zeros(pad, dtype=torch.float32, device=l.weight.device))
+            n += l.out_features + pad
+        return cls(rt, torch.cat(mats, dim=0), torch.cat(biases) if any_bias else None), starts
+
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x [rows, in] in the compute dtype (or a DeferredNorm of float32 rows). With ``residual`` (float32 [rows, out]) the result is

@@ -24,7 +24,7 @@ import torch
 
 from .. import ops
 from ..config.specs import PartSpec
-from .base import Mixer, StateNeed, register_mixer
+from .base import Mixer, StateNeed, own_or_projected, register_mixer
 from .linear import Linear
 
 _NAMES = {"q": "q_proj.weight", "f": "f_proj.weight", "f_bias": "f_proj.bias", "lower": "lower_bound",
@@ -83,10 +83,16 @@ class GatedLinearRecurrence(Mixer):
     def cache_need(self):
         return StateNeed({"S": ((self.n_heads, self.dim, self.v_dim), torch.float32)})
 
+    def input_product(self):
+        return self.proj, "float32"
+
+    def drop_input_product(self):
+        self.proj = None
+
     def forward(self, x, step, cache, residual, write_cache=True):
         nq = self.n_heads * self.dim
-        proj = self.proj(x, out_dtype=torch.float32)                  # [T, q | f | v], bias of f added
-        o = ops.gated_recurrence(proj, 0, nq, 2 * nq, self.lower, self.norm_w, self.eps, cache["S"], step.seg_start,
+        proj, c0 = own_or_projected(self, x, self.proj, torch.float32)   # [T, q | f | v] from column c0, bias of f added
+        o = ops.gated_recurrence(proj, c0, c0 + nq, c0 + 2 * nq, self.lower, self.norm_w, self.eps, cache["S"], step.seg_start,
                                  step.seg_slot, self.n_heads, self.dim, self.v_dim, self.rt.dtype, write_cache, step.max_q_len)
         if residual is None:
             return self.o(o, out_dtype=torch.float32)

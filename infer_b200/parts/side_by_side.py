@@ -45,13 +45,23 @@ class SideBySide(Mixer):
             sub = self.spec[s]
             m.load({local: params[sub.prefix + local] for local in type(m).param_shapes(sub)})
 
+    def members(self):
+        """The two mixers, for a block that joins first products across its parts."""
+        return list(self.sides.values())
+
     def cache_need(self):
         return CompositeNeed({s: m.cache_need() for s, m in self.sides.items()})
 
     def forward_sides(self, x, step, cache, write_cache=True):
         """(first(x), second(x)) as float32, and the two constants: for a block whose sum applies them."""
-        a = self.sides["first"].forward(x, step, cache["first"], None, write_cache)
-        b = self.sides["second"].forward(x, step, cache["second"], None, write_cache)
+        from .base import DeferredNorm, ProjectedInput
+
+        def arg(m):
+            if not isinstance(x, ProjectedInput) or hasattr(m, "input_product"):
+                return x
+            return x.rows_in.materialize() if isinstance(x.rows_in, DeferredNorm) else x.rows_in
+        a = self.sides["first"].forward(arg(self.sides["first"]), step, cache["first"], None, write_cache)
+        b = self.sides["second"].forward(arg(self.sides["second"]), step, cache["second"], None, write_cache)
         return a, b, self.scales["first"], self.scales["second"]
 
     def forward(self, x, step, cache, residual, write_cache=True):
