@@ -32,11 +32,12 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf
 // Short causal filter, per channel: y[t] = sum_j w[c, j] * u[t - (taps - 1) + j]. u before the first row of the
 // step's segment comes from the request's tail (the last taps - 1 values of earlier steps, oldest first; zeros for a
 // new request, which is what "nothing before the start" means). i_local is the token's index within its segment;
-// `col` its channel's column in the rows, `tail` the channel's first tail value, tail_ld the channel count.
+// `col` its channel's column in the rows, `tail` the channel's first tail value, tail_ld the channel count; the
+// channel's tap j is w[j * w_stride].
 template <typename T>
 __device__ __forceinline__ float filtered(const T* __restrict__ rows, int64_t ld, int64_t t, int i_local, int col,
-                                          const float* __restrict__ w, int taps, const T* __restrict__ tail,
-                                          int64_t tail_ld) {
+                                          const float* __restrict__ w, int64_t w_stride, int taps,
+                                          const T* __restrict__ tail, int64_t tail_ld) {
     if (taps <= 1) {
         const float u = ib::to_f32(rows[t * ld + col]);
         return taps == 1 ? w[0] * u : u;
@@ -46,7 +47,7 @@ __device__ __forceinline__ float filtered(const T* __restrict__ rows, int64_t ld
         const int back = taps - 1 - j;
         const float u = i_local >= back ? ib::to_f32(rows[(t - back) * ld + col])
                                         : ib::to_f32(tail[int64_t(taps - 1 + i_local - back) * tail_ld]);
-        y = fmaf(w[j], u, y);
+        y = fmaf(w[j * w_stride], u, y);
     }
     return y;
 }
@@ -63,7 +64,7 @@ __global__ void short_filter_kernel(const T* __restrict__ rows, int64_t ld, int 
     const int c = int(i - t * channels);
     const int s = token_seg[t];
     const T* tail = tails ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c : nullptr;
-    out[i] = ib::from_f32<T>(filtered(rows, ld, t, int(t - seg_start[s]), col0 + c, w + int64_t(c) * taps, taps, tail, channels));
+    out[i] = ib::from_f32<T>(filtered(rows, ld, t, int(t - seg_start[s]), col0 + c, w + int64_t(c) * taps, 1, taps, tail, channels));
 }
 
 // After a step: the tail of every segment's request becomes the last taps - 1 values of (old tail, the step's rows).
@@ -88,7 +89,7 @@ __global__ void filter_tail_kernel(const T* __restrict__ rows, int64_t ld, int c
 
 // ------------------------------------------------------------------------------------------------
 // From projected rows [q heads | k heads | v heads | ...] to what attention reads: optional short filter on every
-// channel, rotation of q and k, optional normalisation of v, q into q_out, k and v into the token's page.
+// channel (its weights tap-major, filt_w[tap][channel], so that neighbouring channels' taps lie side by side), rotation of q and k, optional normalisation of v, q into q_out, k and v into the token's page.
 // Rotation: channels (2i, 2i + 1) of a head, 2i < n_rot, turn by the angle of tables cos/sin [positions, n_rot / 2];
 // the head's other channels stay.  v: each head divided by sqrt(mean(v^2) + eps), no weight.
 // One warp per (token, head of q, k or v); a lane keeps up to PREP_PAIRS pairs of a head in registers.
@@ -130,8 +131,8 @@ qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, int col_base, int inl
         if (2 * p < width) {
             const int c = col0 + 2 * p;                          // channel; its column in the rows is col_base + c
             if (filt) {
-                a[r] = filtered(rows, ld, t, i_local, col_base + c, filt_w + int64_t(c) * taps, taps, tail + c, channels);
-                b[r] = filtered(rows, ld, t, i_local, col_base + c + 1, filt_w + int64_t(c + 1) * taps, taps, tail + c + 1, channels);
+                a[r] = filtered(rows, ld, t, i_local, col_base + c, filt_w + c, channels, taps, tail + c, channels);
+                b[r] = filtered(rows, ld, t, i_local, col_base + c + 1, filt_w + c + 1, channels, taps, tail + c + 1, channels);
                 if (inline_tail && taps > 1) {
                     // one token per request: this lane is the only reader of the two channels' tails; it moves them
                     T* tw = tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c;
@@ -286,14 +287,16 @@ __global__ void head_norm_kernel(const float* __restrict__ o, const float* __res
 // One chunk of staged tokens through a thread's share of the state: the arithmetic of both forms of the kernel.
 // qs, fs: [token][ks][MAXK] (stride kstride); vs: [token][cb]; part: [token][ks][cb].
 template <int MAXK>
-__device__ __forceinline__ void recurrence_chunk(float (&S)[MAXK], const float* qs, const float* fs, const float* vs,
-                                                 float* part, int n, int kstride, int kg, int ks, int cb, int col_l) {
-#pragma unroll 2
+__device__ __forceinline__ void recurrence_chunk(float (&S)[MAXK], const float* __restrict__ qs, const float* __restrict__ fs,
+                                                 const float* __restrict__ vs, float* __restrict__ part, int n, int kstride,
+                                                 int kg, int ks, int cb, int col_l) {
+#pragma unroll 4
     for (int c = 0; c < n; c++) {
         const float v = vs[c * cb + col_l];
         const float4* f4 = reinterpret_cast<const float4*>(fs + c * kstride + kg * MAXK);
         const float4* q4 = reinterpret_cast<const float4*>(qs + c * kstride + kg * MAXK);
-        float acc = 0.0f;
+        // four partial sums (rows 4i, 4i+1, 4i+2, 4i+3), added pairwise at the end: a chain of MAXK / 4 instead of MAXK
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
         for (int k4 = 0; k4 < MAXK / 4; k4++) {
             const float4 f = f4[k4], q = q4[k4];
@@ -301,12 +304,12 @@ __device__ __forceinline__ void recurrence_chunk(float (&S)[MAXK], const float* 
             S[4 * k4 + 1] = fmaf(f.y, S[4 * k4 + 1], (1.0f - f.y) * v);
             S[4 * k4 + 2] = fmaf(f.z, S[4 * k4 + 2], (1.0f - f.z) * v);
             S[4 * k4 + 3] = fmaf(f.w, S[4 * k4 + 3], (1.0f - f.w) * v);
-            acc = fmaf(S[4 * k4 + 0], q.x, acc);
-            acc = fmaf(S[4 * k4 + 1], q.y, acc);
-            acc = fmaf(S[4 * k4 + 2], q.z, acc);
-            acc = fmaf(S[4 * k4 + 3], q.w, acc);
+            a0 = fmaf(S[4 * k4 + 0], q.x, a0);
+            a1 = fmaf(S[4 * k4 + 1], q.y, a1);
+            a2 = fmaf(S[4 * k4 + 2], q.z, a2);
+            a3 = fmaf(S[4 * k4 + 3], q.w, a3);
         }
-        part[(c * ks + kg) * cb + col_l] = acc;
+        part[(c * ks + kg) * cb + col_l] = (a0 + a1) + (a2 + a3);
     }
 }
 
@@ -445,6 +448,152 @@ gated_recurrence_kernel(const float* __restrict__ proj, int64_t ld, int q_col, i
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The same three for bfloat16 rows whose sizes and addresses allow 16-byte accesses (8 values a thread).
+__device__ __forceinline__ void unpack8(const uint4& u, float (&x)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    return u;
+}
+
+__global__ void gelu_tanh_vec_kernel(const bf16* __restrict__ x, int64_t ld, int col0, int64_t width8, bf16* __restrict__ out,
+                                     int64_t n8) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const int64_t t = i / width8, j = i - t * width8;
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + t * ld + col0 + j * 8), v);
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float z = v[e];
+        v[e] = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = pack8(v);
+}
+
+__global__ void head_gate_vec_kernel(bf16* __restrict__ ctx, const bf16* __restrict__ rows, int64_t ld, int gate_col,
+                                     int64_t n8, int n_heads, int dv8) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const int64_t th = i / dv8;
+    const int64_t t = th / n_heads;
+    const int h = int(th - t * n_heads);
+    const float g = sigmoidf_(__bfloat162float(rows[t * ld + gate_col + h]));
+    float v[8];
+    uint4* p = reinterpret_cast<uint4*>(ctx + i * 8);
+    unpack8(*p, v);
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] *= g;
+    *p = pack8(v);
+}
+
+// One warp per (token, head of q, k or v); lane l takes channels 8 l .. 8 l + 7 of the head (heads of up to 256).
+__global__ void __launch_bounds__(128)
+qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, int inline_tail,
+                       const float* __restrict__ filt_w, int taps, bf16* tails, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, int n_rot, int norm_v, float eps,
+                       const int* __restrict__ positions, const int* __restrict__ token_seg,
+                       const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                       const int* __restrict__ block_table, int64_t max_blocks, bf16* __restrict__ q_out,
+                       bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int64_t n_tokens, int n_heads, int n_kv,
+                       int d, int dv, int page_size, int write_cache, int64_t n_pages, int* status) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int units = n_heads + 2 * n_kv;
+    const int64_t wi = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wi >= n_tokens * units) return;
+    const int64_t t = wi / units;
+    const int u = int(wi - t * units);
+    const int kind = u < n_heads ? 0 : (u < n_heads + n_kv ? 1 : 2);
+    const int head = kind == 0 ? u : (kind == 1 ? u - n_heads : u - n_heads - n_kv);
+    const int width = kind == 2 ? dv : d;
+    const int col0 = kind == 0 ? head * d : (kind == 1 ? n_heads * d + head * d : (n_heads + n_kv) * d + head * dv);
+    const int channels = (n_heads + n_kv) * d + n_kv * dv;
+    const int s = token_seg[t];
+    const int i_local = int(t - seg_start[s]);
+    const int pos = positions[t];
+    const bool mine = 8 * lane < width;
+    const int c = col0 + 8 * lane;                               // first of this lane's channels
+    float x[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) x[e] = 0.0f;
+    if (mine) {
+        if (filt_w != nullptr && taps > 0) {
+            bf16* tail = taps > 1 ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c : nullptr;
+            for (int j = 0; j < taps; j++) {
+                const int back = taps - 1 - j;
+                const bf16* src = i_local >= back ? rows + (t - back) * ld + col_base + c
+                                                  : tail + int64_t(taps - 1 + i_local - back) * channels;
+                float uv[8];
+                unpack8(*reinterpret_cast<const uint4*>(src), uv);
+                const float4 w0 = *reinterpret_cast<const float4*>(filt_w + int64_t(j) * channels + c);
+                const float4 w1 = *reinterpret_cast<const float4*>(filt_w + int64_t(j) * channels + c + 4);
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int e = 0; e < 8; e++) x[e] = fmaf(wv[e], uv[e], x[e]);
+            }
+            if (inline_tail && taps > 1) {
+                for (int idx = 0; idx + 1 < taps - 1; idx++)
+                    *reinterpret_cast<uint4*>(tail + int64_t(idx) * channels) = *reinterpret_cast<const uint4*>(tail + int64_t(idx + 1) * channels);
+                *reinterpret_cast<uint4*>(tail + int64_t(taps - 2) * channels) = *reinterpret_cast<const uint4*>(rows + t * ld + col_base + c);
+            }
+        } else {
+            unpack8(*reinterpret_cast<const uint4*>(rows + t * ld + col_base + c), x);
+        }
+        if (kind != 2 && cos_t) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int p = 4 * lane + i;
+                if (2 * p < n_rot) {
+                    const float cs = cos_t[int64_t(pos) * (n_rot / 2) + p], sn = sin_t[int64_t(pos) * (n_rot / 2) + p];
+                    const float ra = x[2 * i] * cs - x[2 * i + 1] * sn;
+                    const float rb = x[2 * i + 1] * cs + x[2 * i] * sn;
+                    x[2 * i] = ra;
+                    x[2 * i + 1] = rb;
+                }
+            }
+        }
+    }
+    if (kind == 2 && norm_v) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss = fmaf(x[e], x[e], ss);
+        ss = ib::warp_sum(ss);
+        const float f = rsqrtf(ss / float(width) + eps);
+#pragma unroll
+        for (int e = 0; e < 8; e++) x[e] *= f;
+    }
+    if (!mine) return;
+    bf16* dst;
+    if (kind == 0) {
+        dst = q_out + (t * n_heads + head) * d;
+    } else {
+        if (!write_cache) return;
+        const int page = block_table[int64_t(s) * max_blocks + pos / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (status && lane == 0) atomicExch(status, 2);
+            return;
+        }
+        dst = (kind == 1 ? k_cache : v_cache) + ((int64_t(page) * n_kv + head) * page_size + pos % page_size) * width;
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * lane) = pack8(x);
+}
+
 }  // namespace
 
 // ================================================================================================
@@ -501,6 +650,12 @@ IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, int col_base, int inl
         IB_LAUNCH(qkv_prepare_kernel<float>, blocks_for(warps, 4), 128, 0, (const float*)rows, ld, col_base, inline_tail, filt_w, taps, (float*)tails, cos_t, sin_t,
                   n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (float*)q_out,
                   (float*)k_cache, (float*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+    else if (dtype == IB_BF16 && d % 8 == 0 && dv % 8 == 0 && ld % 8 == 0 && col_base % 8 == 0 &&
+             !((uintptr_t(rows) | uintptr_t(tails) | uintptr_t(q_out) | uintptr_t(k_cache) | uintptr_t(v_cache) | uintptr_t(filt_w)) & 15))
+        // (chosen by sizes and addresses, never by the number of rows)
+        IB_LAUNCH(qkv_prepare_vec_kernel, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
+                  n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
+                  (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
     else if (dtype == IB_BF16)
         IB_LAUNCH(qkv_prepare_kernel<bf16>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
                   n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
@@ -516,6 +671,8 @@ IB_EXPORT int ib_head_gate(void* ctx, const void* rows, int64_t ld, int gate_col
     const int64_t n = n_tokens * n_heads * dv;
     if (dtype == IB_F32)
         IB_LAUNCH(head_gate_kernel<float>, blocks_for(n, 256), 256, 0, (float*)ctx, (const float*)rows, ld, gate_col, n_tokens, n_heads, dv);
+    else if (dtype == IB_BF16 && dv % 8 == 0 && !(uintptr_t(ctx) & 15))
+        IB_LAUNCH(head_gate_vec_kernel, blocks_for(n / 8, 256), 256, 0, (bf16*)ctx, (const bf16*)rows, ld, gate_col, n / 8, n_heads, dv / 8);
     else if (dtype == IB_BF16)
         IB_LAUNCH(head_gate_kernel<bf16>, blocks_for(n, 256), 256, 0, (bf16*)ctx, (const bf16*)rows, ld, gate_col, n_tokens, n_heads, dv);
     else
@@ -529,6 +686,8 @@ IB_EXPORT int ib_gelu_tanh(const void* x, int64_t ld, int col0, int64_t width, v
     if (n <= 0) return IB_OK;
     if (dtype == IB_F32)
         IB_LAUNCH(gelu_tanh_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)x, ld, col0, width, (float*)out, n);
+    else if (dtype == IB_BF16 && width % 8 == 0 && ld % 8 == 0 && col0 % 8 == 0 && !((uintptr_t(x) | uintptr_t(out)) & 15))
+        IB_LAUNCH(gelu_tanh_vec_kernel, blocks_for(n / 8, 256), 256, 0, (const bf16*)x, ld, col0, width / 8, (bf16*)out, n / 8);
     else if (dtype == IB_BF16)
         IB_LAUNCH(gelu_tanh_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)x, ld, col0, width, (bf16*)out, n);
     else
@@ -589,7 +748,7 @@ IB_EXPORT int ib_gated_recurrence(float* proj, int64_t ld, int q_col, int f_col,
                                   const float* norm_w, float eps, float* state, const int* seg_start,
                                   const int* seg_slot, void* out, int n_segments, int n_heads, int d, int dv,
                                   int write_state, int out_dtype, cudaStream_t stream, int spread, float* scratch,
-                                  int64_t n_tokens, int sm_count) {
+                                  int64_t n_tokens, int sm_count, int col_block) {
     if (n_segments <= 0) return IB_OK;
     int ks, kpt;
     if (n_heads <= 0 || n_heads > 65535 || !recurrence_split(d, dv, &ks, &kpt))
@@ -604,6 +763,7 @@ IB_EXPORT int ib_gated_recurrence(float* proj, int64_t ld, int q_col, int f_col,
         // CTAs of at least 128 threads (a warp per scheduler) until there is about one CTA per SM.
         const int units = n_segments * n_heads, sms = sm_count > 0 ? sm_count : 148;
         while (cb % 8 == 0 && ks * (cb / 2) >= 128 && units * ((dv + cb / 2 - 1) / (cb / 2)) <= sms) cb /= 2;
+        if (col_block > 0 && col_block <= dv && col_block % 4 == 0) cb = col_block;      // (for measurements)
         pipelined = d == ks * maxk && kpt == maxk && d % 4 == 0 && cb % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 &&
                     f_col % 4 == 0 && v_col % 4 == 0 && !(uintptr_t(proj) & 15);
         IB_LAUNCH(recurrence_gates_kernel, blocks_for(n_tokens * n_heads * d, 256), 256, 0, proj, ld, q_col, f_col, lower, n_tokens, n_heads * d);

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import collections
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -310,7 +311,7 @@ def qkv_prepare(rows: torch.Tensor, filt_w: Optional[torch.Tensor], tails: Optio
                 inline_tail: bool = False) -> torch.Tensor:
     """Projected rows [... | q | k | v | ...] (q at column ``col0``) -> q [T, heads * head_dim] for attention, k and v
     into their pages. ``inline_tail`` (only for steps of one token per request): the kernel also moves the tails.
-    Optional on the way: a short causal filter on every q, k and v channel (``filt_w`` float32 [channels, taps] with
+    Optional on the way: a short causal filter on every q, k and v channel (``filt_w`` float32 [taps, channels] with
     the requests' ``tails`` [slots, taps - 1, channels]); rotation of adjacent channel pairs of q and k over the
     first ``n_rot`` channels of each head (tables float32 [positions, n_rot / 2]); v divided by its root mean square
     per head (``norm_v``). ``step`` gives positions, token_seg, seg_start, seg_slot and the status word."""
@@ -325,9 +326,9 @@ def qkv_prepare(rows: torch.Tensor, filt_w: Optional[torch.Tensor], tails: Optio
     taps = 0
     if filt_w is not None:
         _check(filt_w, "filt_w", torch.float32)
-        if filt_w.shape[0] != C:
-            raise KernelError(f"the filter has {filt_w.shape[0]} channels, the rows {C}")
-        taps = filt_w.shape[1]
+        if filt_w.shape[1] != C:
+            raise KernelError(f"the filter has {filt_w.shape[1]} channels, the rows {C}")
+        taps = filt_w.shape[0]
         if taps > 1:
             _check(tails, "tails", rows.dtype)
             if tuple(tails.shape[1:]) != (taps - 1, C):
@@ -407,6 +408,7 @@ def gated_recurrence_fits(dim: int, v_dim: int) -> bool:
 
 # Segments of more tokens than this go through the form of the recurrence that spreads a head's columns over CTAs.
 RECURRENCE_SPREAD_FROM = 8
+RECURRENCE_COLUMN_BLOCK = int(os.environ.get("INFER_B200_RECURRENCE_COLUMNS", "0"))    # 0: the launcher chooses
 
 
 def gated_recurrence(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, lower: torch.Tensor,
@@ -435,8 +437,8 @@ def gated_recurrence(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, low
     scratch = torch.empty((T, n_heads * v_dim), dtype=torch.float32, device=proj.device) if spread else None
     sm_count = torch.cuda.get_device_properties(proj.device).multi_processor_count if spread else 0
     f = _fn("seq", "ib_gated_recurrence", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 4 +
-            [c_int] * 6 + [c_void_p, c_int, c_void_p, c_int64, c_int])
+            [c_int] * 6 + [c_void_p, c_int, c_void_p, c_int64, c_int, c_int])
     _call(f, proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col), lower.data_ptr(), norm_weight.data_ptr(), float(eps),
           state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, dim, v_dim,
-          int(write_state), dtype_code(out_dtype), _stream(), int(spread), _ptr(scratch), T, sm_count)
+          int(write_state), dtype_code(out_dtype), _stream(), int(spread), _ptr(scratch), T, sm_count, RECURRENCE_COLUMN_BLOCK)
     return out

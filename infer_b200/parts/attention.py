@@ -125,8 +125,9 @@ class Attention(Mixer):
         self.qkv = Linear(self.rt, w, b)
         self.o = Linear(self.rt, params[n["o"]])
         if self.taps > 0:
+            # tap-major [taps, channels]: the prepare kernel reads neighbouring channels' taps side by side
             self.filter_w = torch.cat([params[n["q_filter"]], params[n["k_filter"]], params[n["v_filter"]]], dim=0) \
-                .to(device=self.rt.device, dtype=torch.float32).contiguous()
+                .to(device=self.rt.device, dtype=torch.float32).t().contiguous()
 
     def cache_need(self):
         pages = PagedKVNeed(self.n_kv, self.head_dim, self.window, None if self.v_dim == self.head_dim else self.v_dim)

@@ -54,7 +54,7 @@ def test_short_filter_with_tails_over_steps(dtype, taps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("sizes", [(4, 2, 32, 32, 16), (3, 1, 16, 24, 16), (2, 2, 96, 40, 50), (5, 5, 8, 8, 0)])
+@pytest.mark.parametrize("sizes", [(4, 2, 32, 32, 16), (3, 1, 16, 24, 16), (2, 2, 96, 40, 50), (5, 5, 8, 8, 0), (2, 1, 12, 10, 4), (1, 1, 256, 128, 256)])
 def test_prepare_rotates_normalises_and_fills_the_pages(dtype, sizes):
     from infer_b200.parts.rotary import pair_rotation_tables
     H, G, d, dv, n_rot = sizes
@@ -74,7 +74,7 @@ def test_prepare_rotates_normalises_and_fills_the_pages(dtype, sizes):
     cos = sin = None
     if n_rot:
         cos, sin = (t.to(DEV) for t in pair_rotation_tables(n_rot, 777.0, 64))
-    q = ops.qkv_prepare(rows.to(DEV), fw.to(DEV), tails_cpu.to(DEV), cos, sin, n_rot, True, eps, step, table, k_cache, v_cache,
+    q = ops.qkv_prepare(rows.to(DEV), fw.t().contiguous().to(DEV), tails_cpu.to(DEV), cos, sin, n_rot, True, eps, step, table, k_cache, v_cache,
                         H, G, d, dv)
     assert int(step.status.item()) == 0
     r0 = 0
