@@ -386,6 +386,16 @@ def design_arm(args, pk):
     out = {"design": args.design, "sizes": args.sizes, "batch": args.batch, "context": args.context, "dtype": "bf16",
            "data": "synthetic: random weights, random cache contents, fixed token ids", "peaks": pk["source"], "models": {}}
     T = 2048
+    if args.mode != "all":
+        # one part of one model and a short line: for launch lists and captures of small cases (--layers 2)
+        CONFIG = _preset(DESIGNS[args.design][args.sizes])
+        eng = build_engine(args.layers or len(CONFIG["layers"]), args.batch, max(args.context, T), 2 * (args.steps + args.warmup) + 64)
+        if args.mode == "decode":
+            ms, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, ops.kernel_launches)
+            print(json.dumps({"design": args.design, "mode": "decode", "batch": args.batch, "ms_per_step": round(ms, 4), "gpu_launches": launches}))
+        else:
+            print(json.dumps({"design": args.design, "mode": "prefill", "tokens": T, "ms": round(time_prefill(eng, T, max(1, args.steps), args.warmup), 3)}))
+        return 0
     for label, preset in ((args.design, _preset(DESIGNS[args.design][args.sizes])), ("qwen2", SIZES[args.sizes])):
         CONFIG = preset
         n_all = len(preset["layers"]) if isinstance(preset.get("layers"), list) else preset["num_hidden_layers"]

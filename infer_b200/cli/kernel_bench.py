@@ -6,6 +6,7 @@ bytes the kernel has to read and TFLOP/s of its arithmetic.
     python -m infer_b200.cli.kernel_bench attention --batch 8 --context 2048 --q-len 1 [--heads 12 --kv-heads 2 --head-dim 128]
     python -m infer_b200.cli.kernel_bench rmsnorm --M 8 --K 1536
     python -m infer_b200.cli.kernel_bench layer --M 8 --hidden 1536 --intermediate 8960 --qkv 2048 [--phases 1..4]
+    python -m infer_b200.cli.kernel_bench recurrence --batch 1 --q-len 2048 [--heads 12 --head-dim 64 --v-dim 128]
 
 Inputs rotate over enough copies to exceed the 126 MB L2, as in the model where every layer brings its own weights;
 the launches (one per copy) are captured in a CUDA graph and the replay is timed, so the number is what the kernel
@@ -48,7 +49,7 @@ def _time(fn, n_variants, reps, warmup=3):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["linear", "attention", "rmsnorm", "layer"])
+    ap.add_argument("what", choices=["linear", "attention", "rmsnorm", "layer", "recurrence"])
     ap.add_argument("--M", type=int, default=8)
     ap.add_argument("--N", type=int, default=1536)
     ap.add_argument("--K", type=int, default=1536)
@@ -60,6 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--v-dim", type=int, default=128, help="recurrence: columns of a head's state (its rows are --head-dim)")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0, help="tc: the tile code instead of the planner's (many tokens; 768 with --splits 2, 4 or 8: K slices as a cluster)")
     ap.add_argument("--cluster", type=int, default=0)
@@ -139,6 +141,34 @@ def main(argv=None) -> int:
         flops = 4 * B * nh * hd * (q_len * ctx + q_len * (q_len + 1) / 2)
         out.update(batch=B, context=ctx, q_len=q_len, us_median=round(med, 2), us_min=round(mn, 2),
                    gbs=round(nbytes / med / 1e3, 1), tflops=round(flops / med / 1e6, 2))
+    elif args.what == "recurrence":
+        # the gated linear recurrence over `batch` segments of `q_len` tokens each: gates, scan and the heads' norm
+        # (three launches for prompt portions, one for steps of a few tokens); the rows rotate over copies beyond L2
+        B, n, nh, d, dv = args.batch, args.q_len, args.heads, args.head_dim, args.v_dim
+        ld = 2 * nh * d + nh * dv
+        copies = max(4, min(32, L2 // (B * n * ld * 4) + 1))
+        src = [torch.randn(B * n, ld, device=dev) for _ in range(copies)]
+        rows = [torch.empty_like(t) for t in src]
+        lower, nw = torch.rand(nh * d, device=dev) * 0.9, torch.ones(dv, device=dev)
+        state = torch.zeros(B, nh, d, dv, device=dev)
+        seg_start = torch.arange(0, (B + 1) * n, n, dtype=torch.int32, device=dev)
+        seg_slot = torch.arange(B, dtype=torch.int32, device=dev)
+
+        def run(i):
+            return ops.gated_recurrence(rows[i], 0, nh * d, 2 * nh * d, lower, nw, 1e-6, state, seg_start, seg_slot, nh, d, dv,
+                                        torch.bfloat16, True, n)
+
+        def fresh(i):
+            rows[i].copy_(src[i])                      # (the spread form overwrites its rows with the gates)
+            return run(i)
+        both, _ = _time(fresh, copies, args.reps)
+        only_copy, _ = _time(lambda i: rows[i].copy_(src[i]), copies, args.reps)
+        med = both - only_copy
+        flops = 5.0 * B * n * nh * d * dv
+        nbytes = B * n * ld * 4 + B * n * nh * dv * 2 + 2 * B * nh * d * dv * 4
+        out.update(segments=B, tokens_each=n, heads=nh, dim=d, v_dim=dv, us_median=round(med, 2),
+                   gbs=round(nbytes / med / 1e3, 1), tflops_fp32=round(flops / med / 1e6, 2),
+                   ns_per_token_of_a_segment=round(med * 1e3 / n, 1))
     elif args.what == "layer":
         # what a decode layer does between two attention kernels: o product + residual, norm + gate/up + SwiGLU,
         # down + residual, the next layer's norm + q/k/v product with bias (the norm inside the product where the

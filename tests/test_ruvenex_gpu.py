@@ -221,3 +221,26 @@ def test_trace_program_on_a_model_folder(tmp_path, dtype):
                 r += 1
             pos[rid] = pos.get(rid, 0) + len(toks)
     RC.check(cfg, SEED, torch.float32 if dtype == "float32" else torch.bfloat16, got, ids, what="program")
+
+
+def test_generate_program_on_a_model_folder_and_on_a_preset(tmp_path):
+    """bin/generate picks the model class by config.json; greedy ids in float32 equal the plain implementation's,
+    also with the prompt in portions and few pages. --random builds the design from a preset of the package."""
+    from infer_b200.weights import write_random_model
+    cfg = RC.CASES["p"]
+    model = tmp_path / "model"
+    write_random_model(str(model), cfg, SEED, torch.bfloat16)
+    prompt = RC.random_ids(cfg, 21, 1)
+    want = pr.greedy(cfg, H.as_compute(RC.make_weights(cfg, SEED), torch.float32), prompt, 10)
+    gen = os.path.join(ROOT, "bin", "generate")
+
+    def run(args):
+        proc = subprocess.run([sys.executable, gen] + args, capture_output=True, text=True, timeout=900, cwd=ROOT)
+        assert proc.returncode == 0, (proc.stdout[-1500:], proc.stderr[-1500:])
+        line = next(l for l in proc.stdout.splitlines() if l.startswith("ids:"))
+        return [int(t) for t in line.split()[1:]]
+    ids = ",".join(map(str, prompt))
+    assert run(["0", "10", "--model", str(model), "--dtype", "float32", "--prompt-ids", ids, "--max-seq", "64"]) == want
+    assert run(["0", "10", "--model", str(model), "--dtype", "float32", "--prompt-ids", ids, "--max-seq", "64", "--chunk", "5",
+                "--kv-blocks", "3"]) == want
+    assert len(run(["0", "12", "--random", "tiny-ruvenex", "--max-seq", "64"])) == 12
