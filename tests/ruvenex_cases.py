@@ -38,8 +38,8 @@ CASES: Dict[str, dict] = {
                      _layer(_left(2, 2, 32, 16, None, 32, 7.0, 0.25), {"heads": 2, "dim": 24, "vdim": 56}, 0.5, 0.5, 64),
                      _layer(_left(4, 4, 32, 32, 1, None, 1.0, 0.18), {"heads": 4, "dim": 12, "vdim": 12}, 1.0, 1.0, 64)]},
     # head size 128 with eight query heads on two kv heads; a recurrence state of 64 x 64
-    "r": {"architecture": "Ruvenex", "vocab": 256, "width": 128, "embedding": {"scale": 11.3}, "norm": {"eps": 1e-6},
-          "layers": [_layer(_left(8, 2, 128, 128, 3, 64, 500000.0, 0.09), {"heads": 2, "dim": 64, "vdim": 64}, 0.6, 1.1, 256)]},
+    "r": {"architecture": "Ruvenex", "vocab": 256, "width": 128, "embedding": {"scale": 11.3}, "norm": {"eps": 2e-6},
+          "layers": [_layer(_left(8, 2, 128, 128, 3, 64, 250000.0, 0.09), {"heads": 2, "dim": 64, "vdim": 64}, 0.8, 1.25, 256)]},
 }
 
 

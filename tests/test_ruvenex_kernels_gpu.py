@@ -200,8 +200,8 @@ def test_elementwise_pieces(dtype):
     xs, p, q, r = (torch.randn(T, W, generator=g) for _ in range(4))
     gates = torch.randn(T, 2 * W, generator=g)
     dev = lambda t: t.to(DEV).clone()
-    full = ops.gated_sum(dev(xs), dev(gates), dev(p), 0.6, dev(q), 1.1, dev(r)).cpu()
-    want = xs + torch.sigmoid(gates[:, :W]) * (0.6 * p + 1.1 * q) + torch.sigmoid(gates[:, W:]) * r
+    full = ops.gated_sum(dev(xs), dev(gates), dev(p), 0.7, dev(q), 1.3, dev(r)).cpu()
+    want = xs + torch.sigmoid(gates[:, :W]) * (0.7 * p + 1.3 * q) + torch.sigmoid(gates[:, W:]) * r
     assert torch.allclose(full, want, rtol=1e-5, atol=1e-5)
     one = ops.gated_sum(dev(xs), dev(gates[:, :W].contiguous()), dev(p), 2.0).cpu()
     assert torch.allclose(one, xs + torch.sigmoid(gates[:, :W]) * 2.0 * p, rtol=1e-5, atol=1e-5)
