@@ -130,22 +130,23 @@ qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, int col_base, int inl
         a[r] = b[r] = 0.0f;
         if (2 * p < width) {
             const int c = col0 + 2 * p;                          // channel; its column in the rows is col_base + c
+            const bool two = 2 * p + 1 < width;                  // (a head of odd size ends with half a pair)
             if (filt) {
                 a[r] = filtered(rows, ld, t, i_local, col_base + c, filt_w + c, channels, taps, tail + c, channels);
-                b[r] = filtered(rows, ld, t, i_local, col_base + c + 1, filt_w + c + 1, channels, taps, tail + c + 1, channels);
+                if (two) b[r] = filtered(rows, ld, t, i_local, col_base + c + 1, filt_w + c + 1, channels, taps, tail + c + 1, channels);
                 if (inline_tail && taps > 1) {
                     // one token per request: this lane is the only reader of the two channels' tails; it moves them
                     T* tw = tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c;
                     for (int idx = 0; idx + 1 < taps - 1; idx++) {
                         tw[int64_t(idx) * channels] = tw[int64_t(idx + 1) * channels];
-                        tw[int64_t(idx) * channels + 1] = tw[int64_t(idx + 1) * channels + 1];
+                        if (two) tw[int64_t(idx) * channels + 1] = tw[int64_t(idx + 1) * channels + 1];
                     }
                     tw[int64_t(taps - 2) * channels] = rows[t * ld + col_base + c];
-                    tw[int64_t(taps - 2) * channels + 1] = rows[t * ld + col_base + c + 1];
+                    if (two) tw[int64_t(taps - 2) * channels + 1] = rows[t * ld + col_base + c + 1];
                 }
             } else {
                 a[r] = ib::to_f32(rows[t * ld + col_base + c]);
-                b[r] = ib::to_f32(rows[t * ld + col_base + c + 1]);
+                if (two) b[r] = ib::to_f32(rows[t * ld + col_base + c + 1]);
             }
             if (kind != 2 && cos_t && 2 * p < n_rot) {
                 const float cs = cos_t[int64_t(pos) * (n_rot / 2) + p], sn = sin_t[int64_t(pos) * (n_rot / 2) + p];
@@ -184,7 +185,7 @@ qkv_prepare_kernel(const T* __restrict__ rows, int64_t ld, int col_base, int inl
         const int p = lane + 32 * r;
         if (2 * p < width) {
             dst[2 * p] = ib::from_f32<T>(a[r]);
-            dst[2 * p + 1] = ib::from_f32<T>(b[r]);
+            if (2 * p + 1 < width) dst[2 * p + 1] = ib::from_f32<T>(b[r]);
         }
     }
 }
@@ -640,8 +641,8 @@ IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, int col_base, int inl
                              int64_t n_tokens, int n_heads, int n_kv, int d, int dv, int page_size, int write_cache,
                              int64_t n_pages, int dtype, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
-    if (d <= 0 || dv <= 0 || d % 2 || dv % 2 || d > 64 * PREP_PAIRS || dv > 64 * PREP_PAIRS)
-        return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: head sizes %d / %d must be even and at most %d", d, dv, 64 * PREP_PAIRS);
+    if (d <= 0 || dv <= 0 || d > 64 * PREP_PAIRS || dv > 64 * PREP_PAIRS)
+        return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: head sizes %d / %d must be at most %d", d, dv, 64 * PREP_PAIRS);
     if (n_rot < 0 || n_rot % 2 || n_rot > d) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: %d rotated channels of %d", n_rot, d);
     if (filt_w && taps > 1 && !tails) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: a filter of %d taps needs tails", taps);
     if (n_heads <= 0 || n_kv <= 0 || page_size <= 0) return ib::fail(IB_ERR_ARG, "ib_qkv_prepare: bad sizes");

@@ -110,8 +110,6 @@ def _layer(raw: Mapping[str, Any], i: int) -> RuvenexLayer:
         rot_dims, rot_base = _int(rot, "dims", lw + ".rot", 0), _num(rot, "base", lw + ".rot", positive=True)
         if rot_dims % 2 or rot_dims > dim:
             raise ConfigError(f"config.json: {lw}.rot.dims ({rot_dims}) must be even and at most dim ({dim})")
-    if dim % 2 or vdim % 2:
-        raise ConfigError(f"config.json: {lw}.dim and vdim must be even, got {dim} and {vdim}")
     left = AttentionSide(heads, kv, dim, vdim, taps, rot_dims, rot_base, _num(lraw, "scale", lw))
     rdim = _int(rraw, "dim", rw)
     right = RecurrentSide(_int(rraw, "heads", rw), rdim, _int(rraw, "vdim", rw) if rraw.get("vdim") is not None else rdim)

@@ -58,8 +58,8 @@ class Attention(Mixer):
                 raise ValueError("an attention window must be positive (or None for all keys)")
         if self.n_kv <= 0 or self.n_heads % self.n_kv:
             raise ValueError(f"heads ({self.n_heads}) must be a multiple of kv heads ({self.n_kv})")
-        if self.head_dim <= 0 or self.head_dim % 2:
-            raise ValueError(f"head_dim must be positive and even, got {self.head_dim}")
+        if self.head_dim <= 0:
+            raise ValueError(f"head_dim must be positive, got {self.head_dim}")
         if max(self.head_dim, self.v_dim) > ops.attention_max_head_dim():
             raise ValueError(f"head_dim {self.head_dim} / {self.v_dim} is beyond what the attention kernels take ({ops.attention_max_head_dim()})")
         scale = spec.get("softmax_scale")
@@ -70,11 +70,13 @@ class Attention(Mixer):
         self.value_norm_eps = spec.get("value_norm_eps")
         self.head_gate = bool(spec.get("head_gate", False))
         # anything beyond rotate-and-store goes through the prepare kernel (filter, pair rotation, value norm)
+        if getattr(self.position, "layout", "half") == "half" and self.position is not None and self.head_dim % 2:
+            raise ValueError(f"half-split rotation needs an even head_dim, got {self.head_dim}")
         self.prepared = (self.taps > 0 or self.value_norm_eps is not None or self.v_dim != self.head_dim or self.head_gate
                          or getattr(self.position, "layout", "half") == "pairs")
         if self.prepared:
-            if self.v_dim % 2 or max(self.head_dim, self.v_dim) > ops.qkv_prepare_max_head_dim():
-                raise ValueError(f"the prepare kernel takes even head sizes up to {ops.qkv_prepare_max_head_dim()}, "
+            if max(self.head_dim, self.v_dim) > ops.qkv_prepare_max_head_dim():
+                raise ValueError(f"the prepare kernel takes head sizes up to {ops.qkv_prepare_max_head_dim()}, "
                                  f"got {self.head_dim} / {self.v_dim}")
             if self.position is not None and getattr(self.position, "layout", None) != "pairs":
                 raise ValueError("filters, value norm, gates and other value sizes go with position kind 'rotary_pairs' (or none)")

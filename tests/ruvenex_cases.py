@@ -37,6 +37,10 @@ CASES: Dict[str, dict] = {
                      _layer(_left(3, 1, 48, 48, 2, 8, 1000000.0, 0.2), {"heads": 3, "dim": 8, "vdim": 8}, 1.2, 0.4, None),
                      _layer(_left(2, 2, 32, 16, None, 32, 7.0, 0.25), {"heads": 2, "dim": 24, "vdim": 56}, 0.5, 0.5, 64),
                      _layer(_left(4, 4, 32, 32, 1, None, 1.0, 0.18), {"heads": 4, "dim": 12, "vdim": 12}, 1.0, 1.0, 64)]},
+    # nothing a multiple of eight: odd head sizes (values of 7), a width of 36, five taps, one layer, no feed-forward
+    "s": {"architecture": "Ruvenex", "vocab": 97, "width": 36, "embedding": {"scale": 1.7}, "norm": {"eps": 1e-5},
+          "layers": [_layer(_left(2, 1, 10, 7, 5, 6, 30.0, 0.4), {"heads": 1, "dim": 5, "vdim": 9}, 1.1, 0.9, None),
+                     _layer(_left(3, 3, 9, 11, 2, 8, 30.0, 0.35), {"heads": 2, "dim": 3, "vdim": 3}, 0.9, 1.1, 20)]},
     # head size 128 with eight query heads on two kv heads; a recurrence state of 64 x 64
     "r": {"architecture": "Ruvenex", "vocab": 256, "width": 128, "embedding": {"scale": 11.3}, "norm": {"eps": 2e-6},
           "layers": [_layer(_left(8, 2, 128, 128, 3, 64, 250000.0, 0.09), {"heads": 2, "dim": 64, "vdim": 64}, 0.8, 1.25, 256)]},

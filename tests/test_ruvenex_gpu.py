@@ -31,7 +31,7 @@ def _requests(name, lengths, seed0=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["p", "q", "r"])
+@pytest.mark.parametrize("name", ["p", "q", "r", "s"])
 def test_whole(name, dtype):
     reqs = _requests(name, [5, 17, 33, 70, 1, 2])
     eng = _engine(name, dtype)
@@ -49,7 +49,7 @@ def test_tail_one_by_one(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["p", "q", "r"])
+@pytest.mark.parametrize("name", ["p", "q", "r", "s"])
 def test_portions_of_changing_size(name, dtype):
     reqs = _requests(name, [150, 61], seed0=20)
     got = H.run_trace(_engine(name, dtype), H.trace_portions(reqs))

@@ -54,7 +54,7 @@ def test_short_filter_with_tails_over_steps(dtype, taps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("sizes", [(4, 2, 32, 32, 16), (3, 1, 16, 24, 16), (2, 2, 96, 40, 50), (5, 5, 8, 8, 0), (2, 1, 12, 10, 4), (1, 1, 256, 128, 256)])
+@pytest.mark.parametrize("sizes", [(4, 2, 32, 32, 16), (3, 1, 16, 24, 16), (2, 2, 96, 40, 50), (5, 5, 8, 8, 0), (2, 1, 12, 10, 4), (1, 1, 256, 128, 256), (3, 1, 7, 5, 4)])
 def test_prepare_rotates_normalises_and_fills_the_pages(dtype, sizes):
     from infer_b200.parts.rotary import pair_rotation_tables
     H, G, d, dv, n_rot = sizes
