@@ -324,8 +324,8 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  int page_size, int window, float scale, int64_t n_pages, int* status) {
     ib::pdl_wait();
     extern __shared__ float smem[];
-    float* qs = smem;                      // [head_dim]
-    float* ps = qs + head_dim;             // [AT]
+    float* qs = smem;                      // [head_dim], rounded up to an even count: the 8-byte rows behind stay aligned
+    float* ps = qs + ((head_dim + 1) & ~1);   // [AT]
     int64_t* rowoff = reinterpret_cast<int64_t*>(ps + AT);   // [AT] row of each key in the pages: (page, kv head, place)
     __shared__ float red[32];
 
@@ -699,7 +699,7 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
     if (n_kv <= 0 || n_heads % n_kv) return ib::fail(IB_ERR_ARG, "ib_attention_plain: heads %d not a multiple of kv heads %d", n_heads, n_kv);
     if (n_heads > 65535) return ib::fail(IB_ERR_ARG, "ib_attention_plain: too many heads");
     const dim3 grid{unsigned(n_tokens), unsigned(n_heads), 1u};
-    const size_t smem = size_t(head_dim + AT) * sizeof(float) + AT * sizeof(int64_t) + 8;
+    const size_t smem = size_t(((head_dim + 1) & ~1) + AT) * sizeof(float) + AT * sizeof(int64_t) + 8;
     if (dtype == IB_F32)
         IB_LAUNCH(attention_kernel<float>, grid, AT, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status);
