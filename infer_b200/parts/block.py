@@ -9,10 +9,25 @@ that is two mixers side by side hands over both results and their constants, so 
 the residual sum are one float32 kernel."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .base import Block, DeferredNorm, ProjectedInput, register_block
 from .linear import Linear
+
+
+# INFER_B200_BRANCHES=0: the sublayers of a parallel block one after the other on one stream (for comparisons).
+PARALLEL_BRANCHES = os.environ.get("INFER_B200_BRANCHES", "1") == "1"
+_SIDE_STREAMS = {}
+
+
+def _side_streams(device):
+    """Two side streams per device, shared by all layers (a layer's branches join before the next layer forks)."""
+    key = str(device)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+    return _SIDE_STREAMS[key]
 
 
 def normed_input(norm, consumer, h):
@@ -76,10 +91,31 @@ class ParallelGatedBlock(Block):
             if hasattr(part, "input_product") or hasattr(part, "members"):
                 return x
             return n.materialize() if isinstance(n, DeferredNorm) else n
+        gates, g0 = self.gate.forward(x) if self.gate is not None else (None, 0)
+        # In a decode step every kernel is a few microseconds of latency and the sublayers are independent between the
+        # joined products and the sum: the second mixer and the feed-forward run on two side streams beside the first
+        # mixer (in a captured graph: three branches). Only there: none of a decode step's kernels on the side
+        # streams uses the device's shared workspace.
+        side = _side_streams(h.device) if (PARALLEL_BRANCHES and step.decode_only and hasattr(self.mixer, "forward_sides")) else None
+        if side is not None:
+            main = torch.cuda.current_stream(h.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for st in side:
+                st.wait_event(fork)
+            r = None
+            if self.feed_forward is not None:
+                with torch.cuda.stream(side[1]):
+                    r = self.feed_forward.forward(arg(self.feed_forward), None)
+            p, q, a, b = self.mixer.forward_sides(arg(self.mixer), step, cache, write_cache, side[0])
+            for st in side:
+                done = torch.cuda.Event()
+                done.record(st)
+                main.wait_event(done)
+            return ops.gated_sum(h, gates, p, a, q, b, r, g0)
         if hasattr(self.mixer, "forward_sides"):
             p, q, a, b = self.mixer.forward_sides(arg(self.mixer), step, cache, write_cache)
         else:
             p, q, a, b = self.mixer.forward(arg(self.mixer), step, cache, None, write_cache), None, 1.0, 1.0
         r = self.feed_forward.forward(arg(self.feed_forward), None) if self.feed_forward is not None else None
-        gates, g0 = self.gate.forward(x) if self.gate is not None else (None, 0)
         return ops.gated_sum(h, gates, p, a, q, b, r, g0)

@@ -52,16 +52,22 @@ class SideBySide(Mixer):
     def cache_need(self):
         return CompositeNeed({s: m.cache_need() for s, m in self.sides.items()})
 
-    def forward_sides(self, x, step, cache, write_cache=True):
-        """(first(x), second(x)) as float32, and the two constants: for a block whose sum applies them."""
+    def forward_sides(self, x, step, cache, write_cache=True, side_stream=None):
+        """(first(x), second(x)) as float32, and the two constants: for a block whose sum applies them. With
+        ``side_stream`` the second mixer's kernels go to that stream (the two read the same rows and write nothing in
+        common); the caller has made it wait for the rows and waits for ``side_stream`` before it reads the result."""
         from .base import DeferredNorm, ProjectedInput
 
         def arg(m):
             if not isinstance(x, ProjectedInput) or hasattr(m, "input_product"):
                 return x
             return x.rows_in.materialize() if isinstance(x.rows_in, DeferredNorm) else x.rows_in
+        if side_stream is not None:
+            with torch.cuda.stream(side_stream):
+                b = self.sides["second"].forward(arg(self.sides["second"]), step, cache["second"], None, write_cache)
         a = self.sides["first"].forward(arg(self.sides["first"]), step, cache["first"], None, write_cache)
-        b = self.sides["second"].forward(arg(self.sides["second"]), step, cache["second"], None, write_cache)
+        if side_stream is None:
+            b = self.sides["second"].forward(arg(self.sides["second"]), step, cache["second"], None, write_cache)
         return a, b, self.scales["first"], self.scales["second"]
 
     def forward(self, x, step, cache, residual, write_cache=True):
