@@ -3,7 +3,7 @@ when the kernel does not take the shape, in which case the caller uses the plain
 
 Kernels that need scratch memory (split-K partial tiles, flash-decoding partial results) share one
 workspace per device, allocated once and grown on demand; calls on one stream run in order, so they
-may share it.  One status word per device collects failures that kernels report (a page index out of
+may share it (a registered side stream has its own).  One status word per device collects failures that kernels report (a page index out of
 range, a bounded wait that ran out).
 """
 from __future__ import annotations
@@ -47,12 +47,29 @@ class DeviceState:
 
 
 _STATES: Dict[torch.device, DeviceState] = {}
+_SIDE_STATES: Dict[tuple, DeviceState] = {}        # (device, raw handle of a registered side stream) -> its scratch
+
+
+def register_side_stream(stream: "torch.cuda.Stream") -> None:
+    """A stream on which a part runs kernels beside those of the step's own stream. Kernels launched while it is the
+    current stream get a workspace and counters of their own (calls on ONE stream run in order and may share
+    scratch; calls on two streams may not). The status word stays one per device."""
+    device = torch.device("cuda", stream.device_index if hasattr(stream, "device_index") else stream.device.index)
+    key = (device, stream.cuda_stream)
+    if key not in _SIDE_STATES:
+        st = DeviceState(device)
+        st.status = device_state(device).status
+        _SIDE_STATES[key] = st
 
 
 def device_state(device) -> DeviceState:
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
+    if _SIDE_STATES:
+        side = _SIDE_STATES.get((device, torch._C._cuda_getCurrentRawStream(device.index)))
+        if side is not None:
+            return side
     st = _STATES.get(device)
     if st is None:
         st = _STATES[device] = DeviceState(device)

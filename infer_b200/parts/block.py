@@ -26,7 +26,10 @@ def _side_streams(device):
     """Two side streams per device, shared by all layers (a layer's branches join before the next layer forks)."""
     key = str(device)
     if key not in _SIDE_STREAMS:
+        from .. import fast_ops
         _SIDE_STREAMS[key] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+        for st in _SIDE_STREAMS[key]:
+            fast_ops.register_side_stream(st)
     return _SIDE_STREAMS[key]
 
 
@@ -92,10 +95,12 @@ class ParallelGatedBlock(Block):
                 return x
             return n.materialize() if isinstance(n, DeferredNorm) else n
         gates, g0 = self.gate.forward(x) if self.gate is not None else (None, 0)
-        # In a decode step every kernel is a few microseconds of latency and the sublayers are independent between the
-        # joined products and the sum: the second mixer and the feed-forward run on two side streams beside the first
-        # mixer (in a captured graph: three branches). Only there: none of a decode step's kernels on the side
-        # streams uses the device's shared workspace.
+        # The sublayers are independent between the joined products and the sum. In a decode step every kernel is a few
+        # microseconds of latency, so the second mixer and the feed-forward run on two side streams beside the first
+        # mixer (in a captured graph: three branches), and three chains of two to four kernels take the time of the
+        # longest. Not in steps with prompt portions: measured on a 2,048-token prompt, the recurrence's scan beside
+        # the persistent products (which count on an SM each) made the step 33 ms instead of 18. The fast kernels'
+        # scratch is per side stream (fast_ops.register_side_stream).
         side = _side_streams(h.device) if (PARALLEL_BRANCHES and step.decode_only and hasattr(self.mixer, "forward_sides")) else None
         if side is not None:
             main = torch.cuda.current_stream(h.device)
