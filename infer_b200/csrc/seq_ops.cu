@@ -503,7 +503,35 @@ __global__ void head_gate_vec_kernel(bf16* __restrict__ ctx, const bf16* __restr
     *p = pack8(v);
 }
 
-// One warp per (token, head of q, k or v); lane l takes channels 8 l .. 8 l + 7 of the head (heads of up to 256).
+// V bfloat16 values (V = 4 or 8) as one 8- or 16-byte access.
+template <int V> struct VecOf;
+template <> struct VecOf<8> { using type = uint4; };
+template <> struct VecOf<4> { using type = uint2; };
+
+template <int V>
+__device__ __forceinline__ void load_bf16(const bf16* p, float (&x)[V]) {
+    const typename VecOf<V>::type u = *reinterpret_cast<const typename VecOf<V>::type*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < V / 2; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
+template <int V>
+__device__ __forceinline__ void store_bf16(bf16* p, const float (&x)[V]) {
+    typename VecOf<V>::type u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < V / 2; i++) h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    *reinterpret_cast<typename VecOf<V>::type*>(p) = u;
+}
+
+// One warp per (token, head of q, k or v); lane l takes channels V l .. V l + V - 1 of the head: V = 4 for heads of up
+// to 128 channels (every lane of a 128-wide head has work), V = 8 for heads of up to 256.
+template <int V>
 __global__ void __launch_bounds__(128)
 qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, int inline_tail,
                        const float* __restrict__ filt_w, int taps, bf16* tails, const float* __restrict__ cos_t,
@@ -514,6 +542,7 @@ qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, 
                        bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int64_t n_tokens, int n_heads, int n_kv,
                        int d, int dv, int page_size, int write_cache, int64_t n_pages, int* status) {
     ib::pdl_wait();
+    using Vec = typename VecOf<V>::type;
     const int lane = threadIdx.x & 31;
     const int units = n_heads + 2 * n_kv;
     const int64_t wi = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -528,11 +557,11 @@ qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, 
     const int s = token_seg[t];
     const int i_local = int(t - seg_start[s]);
     const int pos = positions[t];
-    const bool mine = 8 * lane < width;
-    const int c = col0 + 8 * lane;                               // first of this lane's channels
-    float x[8];
+    const bool mine = V * lane < width;
+    const int c = col0 + V * lane;                               // first of this lane's channels
+    float x[V];
 #pragma unroll
-    for (int e = 0; e < 8; e++) x[e] = 0.0f;
+    for (int e = 0; e < V; e++) x[e] = 0.0f;
     if (mine) {
         if (filt_w != nullptr && taps > 0) {
             bf16* tail = taps > 1 ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels + c : nullptr;
@@ -540,26 +569,30 @@ qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, 
                 const int back = taps - 1 - j;
                 const bf16* src = i_local >= back ? rows + (t - back) * ld + col_base + c
                                                   : tail + int64_t(taps - 1 + i_local - back) * channels;
-                float uv[8];
-                unpack8(*reinterpret_cast<const uint4*>(src), uv);
-                const float4 w0 = *reinterpret_cast<const float4*>(filt_w + int64_t(j) * channels + c);
-                const float4 w1 = *reinterpret_cast<const float4*>(filt_w + int64_t(j) * channels + c + 4);
-                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                float uv[V];
+                load_bf16<V>(src, uv);
+                const float4* w4 = reinterpret_cast<const float4*>(filt_w + int64_t(j) * channels + c);
 #pragma unroll
-                for (int e = 0; e < 8; e++) x[e] = fmaf(wv[e], uv[e], x[e]);
+                for (int e4 = 0; e4 < V / 4; e4++) {
+                    const float4 w = w4[e4];
+                    x[4 * e4 + 0] = fmaf(w.x, uv[4 * e4 + 0], x[4 * e4 + 0]);
+                    x[4 * e4 + 1] = fmaf(w.y, uv[4 * e4 + 1], x[4 * e4 + 1]);
+                    x[4 * e4 + 2] = fmaf(w.z, uv[4 * e4 + 2], x[4 * e4 + 2]);
+                    x[4 * e4 + 3] = fmaf(w.w, uv[4 * e4 + 3], x[4 * e4 + 3]);
+                }
             }
             if (inline_tail && taps > 1) {
                 for (int idx = 0; idx + 1 < taps - 1; idx++)
-                    *reinterpret_cast<uint4*>(tail + int64_t(idx) * channels) = *reinterpret_cast<const uint4*>(tail + int64_t(idx + 1) * channels);
-                *reinterpret_cast<uint4*>(tail + int64_t(taps - 2) * channels) = *reinterpret_cast<const uint4*>(rows + t * ld + col_base + c);
+                    *reinterpret_cast<Vec*>(tail + int64_t(idx) * channels) = *reinterpret_cast<const Vec*>(tail + int64_t(idx + 1) * channels);
+                *reinterpret_cast<Vec*>(tail + int64_t(taps - 2) * channels) = *reinterpret_cast<const Vec*>(rows + t * ld + col_base + c);
             }
         } else {
-            unpack8(*reinterpret_cast<const uint4*>(rows + t * ld + col_base + c), x);
+            load_bf16<V>(rows + t * ld + col_base + c, x);
         }
         if (kind != 2 && cos_t) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int p = 4 * lane + i;
+            for (int i = 0; i < V / 2; i++) {
+                const int p = (V / 2) * lane + i;
                 if (2 * p < n_rot) {
                     const float cs = cos_t[int64_t(pos) * (n_rot / 2) + p], sn = sin_t[int64_t(pos) * (n_rot / 2) + p];
                     const float ra = x[2 * i] * cs - x[2 * i + 1] * sn;
@@ -573,11 +606,11 @@ qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, 
     if (kind == 2 && norm_v) {
         float ss = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 8; e++) ss = fmaf(x[e], x[e], ss);
+        for (int e = 0; e < V; e++) ss = fmaf(x[e], x[e], ss);
         ss = ib::warp_sum(ss);
         const float f = rsqrtf(ss / float(width) + eps);
 #pragma unroll
-        for (int e = 0; e < 8; e++) x[e] *= f;
+        for (int e = 0; e < V; e++) x[e] *= f;
     }
     if (!mine) return;
     bf16* dst;
@@ -592,7 +625,7 @@ qkv_prepare_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int col_base, 
         }
         dst = (kind == 1 ? k_cache : v_cache) + ((int64_t(page) * n_kv + head) * page_size + pos % page_size) * width;
     }
-    *reinterpret_cast<uint4*>(dst + 8 * lane) = pack8(x);
+    store_bf16<V>(dst + V * lane, x);
 }
 
 }  // namespace
@@ -653,10 +686,17 @@ IB_EXPORT int ib_qkv_prepare(const void* rows, int64_t ld, int col_base, int inl
                   (float*)k_cache, (float*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
     else if (dtype == IB_BF16 && d % 8 == 0 && dv % 8 == 0 && ld % 8 == 0 && col_base % 8 == 0 &&
              !((uintptr_t(rows) | uintptr_t(tails) | uintptr_t(q_out) | uintptr_t(k_cache) | uintptr_t(v_cache) | uintptr_t(filt_w)) & 15))
+    {
         // (chosen by sizes and addresses, never by the number of rows)
-        IB_LAUNCH(qkv_prepare_vec_kernel, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
-                  n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
-                  (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+        if (d <= 128 && dv <= 128)
+            IB_LAUNCH(qkv_prepare_vec_kernel<4>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
+                      n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
+                      (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+        else
+            IB_LAUNCH(qkv_prepare_vec_kernel<8>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
+                      n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
+                      (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+    }
     else if (dtype == IB_BF16)
         IB_LAUNCH(qkv_prepare_kernel<bf16>, blocks_for(warps, 4), 128, 0, (const bf16*)rows, ld, col_base, inline_tail, filt_w, taps, (bf16*)tails, cos_t, sin_t,
                   n_rot, norm_v, eps, positions, token_seg, seg_start, seg_slot, block_table, max_blocks, (bf16*)q_out,
