@@ -30,6 +30,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
     "seq": "seq_ops.cu",         # filters over time, pair rotation, gated recurrence, side-by-side sublayers
+    "mix": "mix_ops.cu",         # norms on sublayer results, decayed and delta-rule recurrences, routers, row norms of q and k
     "gemvb": "gemv_bulk.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",

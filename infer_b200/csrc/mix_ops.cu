@@ -1,0 +1,740 @@
+// Kernels for layers that normalise what a sublayer returns, for linear recurrences with a matrix state per head
+// (a decay per key channel; the gated delta rule), for whole-row query/key norms in front of paged attention, and
+// for routed feed-forwards (router, clipped gated activations).
+//
+// Storage of activations is float or bfloat16 (template parameter), arithmetic float. Norms, routers, decays and
+// their logarithms, step sizes, unit norms, recurrent state and the residual sum are float in both. With float
+// storage these kernels are the 32-bit path.
+//
+// A step's rows are the tokens of several requests ("segments") one after the other: seg_start[s] is the first row
+// of segment s, seg_slot[s] the request's state slot. A token's result depends on its own request's earlier tokens
+// and state only, and every sum runs in an order fixed by the layer's sizes: results do not depend on how a prompt
+// was cut or on what else is in the step.
+#include "common.cuh"
+
+IB_DEFINE_LAST_ERROR()
+
+#define IB_LAUNCH(kernel, grid, block, smem, ...)                                                              \
+    do {                                                                                                       \
+        const int rc_ = ib::launch(#kernel, kernel, dim3(grid), dim3(block), size_t(smem), stream, 1u, __VA_ARGS__); \
+        if (rc_) return rc_;                                                                                   \
+    } while (0)
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + threads - 1) / threads); }
+
+__device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float log_sigmoid_(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
+
+// ------------------------------------------------------------------------------------------------
+// out = x + y / sqrt(mean(y^2) + eps) * w per row (x absent: the norm alone), float; optionally a copy of the result
+// in the compute dtype for the next sublayer's first matrix product. One CTA per row. x and out may be one buffer.
+template <typename TC>
+__global__ void __launch_bounds__(256)
+norm_add_kernel(const float* x, const float* __restrict__ y, const float* __restrict__ w, float eps, float* out,
+                TC* __restrict__ copy, int64_t width) {
+    ib::pdl_wait();
+    __shared__ float red[32];
+    const int64_t t = blockIdx.x;
+    const float* yr = y + t * width;
+    float ss = 0.0f;
+    for (int64_t i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+    ss = ib::block_sum(ss, red);
+    const float f = 1.0f / sqrtf(ss / float(width) + eps);
+    for (int64_t i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = yr[i] * f * w[i];
+        if (x) v += x[t * width + i];
+        out[t * width + i] = v;
+        if (copy) copy[t * width + i] = ib::from_f32<TC>(v);
+    }
+}
+
+// Float rows in the compute dtype (for a sublayer that reads the residual stream itself).
+template <typename TC>
+__global__ void cast_rows_kernel(const float* __restrict__ x, TC* __restrict__ out, int64_t n) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = ib::from_f32<TC>(x[i]);
+}
+
+// m = sa * a / rms(a) * wa + sb * b / rms(b) * wb per row (two sublayers side by side, each normalised over the
+// width); then, with wo given, out = x + m / rms(m) * wo and the compute-dtype copy, as norm_add does: the layer's
+// whole tail in one pass over the rows. Without wo: out = m.
+template <typename TC>
+__global__ void __launch_bounds__(256)
+dual_norm_sum_kernel(const float* __restrict__ a, const float* __restrict__ wa, float sa, const float* __restrict__ b,
+                     const float* __restrict__ wb, float sb, float eps, const float* x, const float* __restrict__ wo,
+                     float eps_o, float* out, TC* __restrict__ copy, int64_t width) {
+    ib::pdl_wait();
+    extern __shared__ float row[];           // [width]
+    __shared__ float red[32];
+    const int64_t t = blockIdx.x;
+    const float* ar = a + t * width;
+    const float* br = b + t * width;
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int64_t i = threadIdx.x; i < width; i += blockDim.x) {
+        s1 = fmaf(ar[i], ar[i], s1);
+        s2 = fmaf(br[i], br[i], s2);
+    }
+    s1 = ib::block_sum(s1, red);
+    s2 = ib::block_sum(s2, red);
+    const float fa = sa / sqrtf(s1 / float(width) + eps), fb = sb / sqrtf(s2 / float(width) + eps);
+    float s3 = 0.0f;
+    for (int64_t i = threadIdx.x; i < width; i += blockDim.x) {
+        const float m = ar[i] * fa * wa[i] + br[i] * fb * wb[i];
+        row[i] = m;
+        s3 = fmaf(m, m, s3);
+    }
+    if (!wo) {
+        for (int64_t i = threadIdx.x; i < width; i += blockDim.x) out[t * width + i] = row[i];
+        return;
+    }
+    s3 = ib::block_sum(s3, red);
+    const float fo = 1.0f / sqrtf(s3 / float(width) + eps_o);
+    for (int64_t i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = row[i] * fo * wo[i];
+        if (x) v += x[t * width + i];
+        out[t * width + i] = v;
+        if (copy) copy[t * width + i] = ib::from_f32<TC>(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Gated activations of a feed-forward's hidden layer: columns [gate_col, gate_col + width) and [up_col, ...) of the
+// rows -> out [tokens, width] contiguous.
+//   kind 0: gelu_tanh(g) * u
+//   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(slope * g') * (u' + 1)
+// Columns are cut into blocks of `group` (an expert's hidden size): block e of token t is multiplied by
+// scale[t * n_groups + e] (a router's weight, zero for an expert the token does not use); columns from
+// n_groups * group on (a shared expert) are not scaled and use limit2.
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ rows, int64_t ld, int64_t gate_col, int64_t up_col, int64_t width,
+                               int kind, float limit, float limit2, float slope, const float* __restrict__ scale,
+                               int64_t group, int64_t n_groups, T* __restrict__ out, int64_t n) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t t = i / width, c = i - t * width;
+    float g = ib::to_f32(rows[t * ld + gate_col + c]);
+    float u = ib::to_f32(rows[t * ld + up_col + c]);
+    float y;
+    if (kind == 0) {
+        y = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    } else {
+        const int64_t e = group > 0 ? c / group : 0;
+        const float lim = (group > 0 && e >= n_groups) ? limit2 : limit;
+        g = fminf(g, lim);
+        u = fminf(fmaxf(u, -lim), lim);
+        y = g * sigmoid_(slope * g) * (u + 1.0f);
+        if (scale && e < n_groups) y *= scale[t * n_groups + e];
+    }
+    out[i] = ib::from_f32<T>(y);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Router: scores = softmax(logits) over all experts; experts form n_groups groups of neighbours, a group's score is
+// its largest; only experts of the `keep` best groups can be chosen; the `top` largest of those are chosen (ties:
+// the lower index); their weights are their scores divided by (their sum + sum_eps). One warp per token.
+// weights [tokens, experts]: a chosen expert's weight, zero elsewhere. chosen [tokens, top] (optional): the indices.
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ logits, int64_t n_tokens, int n_experts, int top, int n_groups, int keep,
+             float sum_eps, float* __restrict__ weights, int* __restrict__ chosen) {
+    ib::pdl_wait();
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t t = int64_t(blockIdx.x) * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    float* s = sm + warp * (n_experts + n_groups);          // scores; a chosen expert's score becomes -(1 + score)
+    float* gs = s + n_experts;                               // group scores; -1: a kept group, -2: not kept
+    const float* z = logits + t * n_experts;
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+    mx = ib::warp_max(mx);
+    float sum = 0.0f;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float v = expf(z[e] - mx);
+        s[e] = v;
+        sum += v;
+    }
+    sum = ib::warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < n_experts; e += 32) s[e] = s[e] / sum;
+    __syncwarp();
+    const int per = n_experts / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+        float m = -1.0f;
+        for (int j = 0; j < per; j++) m = fmaxf(m, s[g * per + j]);
+        gs[g] = m;
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; r++) {
+        float best = -1.0f;
+        int at = 0x7fffffff;
+        for (int g = lane; g < n_groups; g += 32)
+            if (gs[g] > best) { best = gs[g]; at = g; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (lane == 0 && at < n_groups) gs[at] = -1.0f - 1.0f;   // kept (marked below as -1 after the loop)
+        __syncwarp();
+    }
+    // a kept group now holds -2, every other its score >= 0
+    float total = 0.0f;
+    for (int r = 0; r < top; r++) {
+        float best = -1.0f;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32)
+            if (gs[e / per] < -1.5f && s[e] > best) { best = s[e]; at = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at < n_experts) {
+            total += best;
+            if (lane == 0) {
+                s[at] = -1.0f - best;
+                if (chosen) chosen[t * top + r] = at;
+            }
+        } else if (lane == 0 && chosen) {
+            chosen[t * top + r] = -1;
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / (total + sum_eps);
+    for (int e = lane; e < n_experts; e += 32) weights[t * n_experts + e] = s[e] < 0.0f ? (-1.0f - s[e]) * inv : 0.0f;
+}
+
+// ------------------------------------------------------------------------------------------------
+// In front of paged attention: projected rows [q | k | v] (q at column col0) -> q rows for the attention kernel, k and
+// v into the token's page. q is normalised over ALL its heads * d channels at once, with a weight per channel (wq),
+// k likewise (wk); a null weight leaves that projection as it is. One CTA per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rownorm_store_kernel(const T* __restrict__ rows, int64_t ld, int col0, const float* __restrict__ wq,
+                     const float* __restrict__ wk, float eps, const int* __restrict__ positions,
+                     const int* __restrict__ token_seg, const int* __restrict__ block_table, int64_t max_blocks,
+                     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, int n_heads, int n_kv, int d,
+                     int dv, int page_size, int write_cache, int64_t n_pages, int* status) {
+    ib::pdl_wait();
+    __shared__ float red[32];
+    const int64_t t = blockIdx.x;
+    const int nq = n_heads * d, nk = n_kv * d, nv = n_kv * dv;
+    const T* r = rows + t * ld + col0;
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = ib::to_f32(r[i]); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = ib::to_f32(r[nq + i]); sk = fmaf(v, v, sk); }
+    sq = ib::block_sum(sq, red);
+    sk = ib::block_sum(sk, red);
+    const float fq = 1.0f / sqrtf(sq / float(nq) + eps), fk = 1.0f / sqrtf(sk / float(nk) + eps);
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const float v = ib::to_f32(r[i]);
+        q_out[t * nq + i] = wq ? ib::from_f32<T>(v * fq * wq[i]) : r[i];
+    }
+    if (!write_cache) return;
+    const int pos = positions[t];
+    const int page = block_table[int64_t(token_seg[t]) * max_blocks + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+        if (status && threadIdx.x == 0) atomicExch(status, 2);
+        return;
+    }
+    const int place = pos % page_size;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int h = i / d, j = i - h * d;
+        const float v = ib::to_f32(r[nq + i]);
+        k_cache[((int64_t(page) * n_kv + h) * page_size + place) * d + j] = wk ? ib::from_f32<T>(v * fk * wk[i]) : r[nq + i];
+    }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const int h = i / dv, j = i - h * dv;
+        v_cache[((int64_t(page) * n_kv + h) * page_size + place) * dv + j] = r[nq + nk + i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decays of a linear attention whose key channels forget at learned, input-dependent rates:
+//   z[t, c] = bias[c] + sum_r up[c, r] * low[t, r]      (low: the rows' columns [low_col, low_col + rank), float)
+//   decay[t, c] = sigmoid(z) ^ (1 / tau) = exp(log_sigmoid(z) / tau)
+// and, in the same pass, q[t, c] *= q_scale in place (columns [q_col, q_col + channels) of the rows).
+__global__ void decay_gates_kernel(float* __restrict__ rows, int64_t ld, int q_col, int low_col, int rank,
+                                   const float* __restrict__ up, const float* __restrict__ bias, float inv_tau, float q_scale,
+                                   float* __restrict__ decay, int64_t n_tokens, int channels) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * channels) return;
+    const int64_t t = i / channels;
+    const int c = int(i - t * channels);
+    const float* low = rows + t * ld + low_col;
+    const float* u = up + int64_t(c) * rank;
+    float z = 0.0f;
+    for (int r = 0; r < rank; r++) z = fmaf(u[r], low[r], z);
+    z += bias ? bias[c] : 0.0f;
+    decay[i] = expf(log_sigmoid_(z) * inv_tau);
+    rows[t * ld + q_col + c] *= q_scale;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Short causal filter per channel: y[t] = sum_j w[j][c] * u[t - (taps - 1) + j]; u before the segment's first row
+// comes from the request's tail (its last taps - 1 inputs, oldest first; zeros for a new request). Weights tap-major.
+__device__ __forceinline__ float filtered(const float* __restrict__ rows, int64_t ld, int64_t t, int i_local, int col,
+                                          const float* __restrict__ w, int64_t w_stride, int taps,
+                                          const float* __restrict__ tail, int64_t tail_ld) {
+    if (taps <= 0 || !w) return rows[t * ld + col];
+    float y = 0.0f;
+    for (int j = 0; j < taps; j++) {
+        const int back = taps - 1 - j;
+        const float u = i_local >= back ? rows[(t - back) * ld + col] : tail[int64_t(taps - 1 + i_local - back) * tail_ld];
+        y = fmaf(w[j * w_stride], u, y);
+    }
+    return y;
+}
+
+// What the gated delta rule reads, from the projected rows (float): raw columns from col0 are [q (G heads of d) |
+// k (G x d) | v (H heads of dv)], each channel through its causal filter and silu; q and k of a head divided by
+// sqrt(sum(x^2) + unit_eps), q also times q_scale; per head h: beta = sigmoid(raw[b_col + h]),
+// g = exp(-exp(a_log[h]) * softplus(raw[a_col + h] + dt_bias[h])).
+// prep rows (float, ldp): [q | k | v | g (H) | beta (H) | k.q (G)].
+// One warp per (token, unit): G units of a (q, k) head pair, H units of a v head, one unit for the heads' scalars.
+constexpr int PREP_PER_LANE = 8;         // heads of up to 32 * PREP_PER_LANE channels
+
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const float* __restrict__ rows, int64_t ld, int col0, int a_col, int b_col,
+                     const float* __restrict__ filt_w, int taps, const float* __restrict__ tails,
+                     const float* __restrict__ a_log, const float* __restrict__ dt_bias, float unit_eps, float q_scale,
+                     const int* __restrict__ token_seg, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                     float* __restrict__ prep, int64_t ldp, int64_t n_tokens, int n_heads, int n_qk, int d, int dv) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int units = n_qk + n_heads + 1;
+    const int64_t wi = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wi >= n_tokens * units) return;
+    const int64_t t = wi / units;
+    const int u = int(wi - t * units);
+    const int channels = 2 * n_qk * d + n_heads * dv;
+    const int s = token_seg[t];
+    const int i_local = int(t - seg_start[s]);
+    const float* tail = taps > 1 ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels : nullptr;
+    float* out = prep + t * ldp;
+    const int g_off = 2 * n_qk * d + n_heads * dv;
+    if (u < n_qk) {
+        float qv[PREP_PER_LANE], kv[PREP_PER_LANE];
+        float sq = 0.0f, sk = 0.0f, dot = 0.0f;
+#pragma unroll
+        for (int r = 0; r < PREP_PER_LANE; r++) {
+            const int j = lane + 32 * r;
+            qv[r] = kv[r] = 0.0f;
+            if (j < d) {
+                const int cq = u * d + j, ck = n_qk * d + u * d + j;
+                qv[r] = silu_(filtered(rows, ld, t, i_local, col0 + cq, filt_w + cq, channels, taps, tail + cq, channels));
+                kv[r] = silu_(filtered(rows, ld, t, i_local, col0 + ck, filt_w + ck, channels, taps, tail + ck, channels));
+                sq = fmaf(qv[r], qv[r], sq);
+                sk = fmaf(kv[r], kv[r], sk);
+                dot = fmaf(qv[r], kv[r], dot);
+            }
+        }
+        sq = ib::warp_sum(sq);
+        sk = ib::warp_sum(sk);
+        dot = ib::warp_sum(dot);
+        const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.0f / sqrtf(sk + unit_eps);
+#pragma unroll
+        for (int r = 0; r < PREP_PER_LANE; r++) {
+            const int j = lane + 32 * r;
+            if (j < d) {
+                out[u * d + j] = qv[r] * fq;
+                out[n_qk * d + u * d + j] = kv[r] * fk;
+            }
+        }
+        if (lane == 0) out[g_off + 2 * n_heads + u] = dot * fq * fk;
+    } else if (u < n_qk + n_heads) {
+        const int h = u - n_qk;
+        for (int j = lane; j < dv; j += 32) {
+            const int c = 2 * n_qk * d + h * dv + j;
+            out[c] = silu_(filtered(rows, ld, t, i_local, col0 + c, filt_w + c, channels, taps, tail + c, channels));
+        }
+    } else {
+        for (int h = lane; h < n_heads; h += 32) {
+            const float a = rows[t * ld + a_col + h], b = rows[t * ld + b_col + h];
+            out[g_off + h] = expf(-expf(a_log[h]) * softplus_(a + dt_bias[h]));
+            out[g_off + n_heads + h] = sigmoid_(b);
+        }
+    }
+}
+
+// After a step: the tail of every segment's request becomes the last taps - 1 values of (old tail, the step's rows).
+// One thread per (segment, channel) moves its values oldest first, reading ahead of what it writes.
+__global__ void tail_update_kernel(const float* __restrict__ rows, int64_t ld, int col0, int channels, int taps,
+                                   float* __restrict__ tails, const int* __restrict__ seg_start,
+                                   const int* __restrict__ seg_slot) {
+    ib::pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = blockIdx.y;
+    if (c >= channels) return;
+    const int keep = taps - 1;
+    const int64_t t0 = seg_start[s];
+    const int len = int(seg_start[s + 1] - t0);
+    float* tail = tails + (int64_t(seg_slot[s]) * keep) * channels + c;
+    for (int idx = 0; idx < keep; idx++) {
+        const int src = len - keep + idx;
+        tail[int64_t(idx) * channels] = src >= 0 ? rows[(t0 + src) * ld + col0 + c] : tail[int64_t(idx + len) * channels];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Linear recurrences with a matrix state S [d, dv] per head (float, kept in `state` between steps), over the tokens of
+// every segment in order:
+//   MODE 0 (a decay per key channel):  S <- diag(a_t) S + k_t v_t^T;               o_t = S^T q_t
+//   MODE 1 (gated delta rule):         S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+// MODE 1 is computed from the old state in one sweep: r = S^T k, p = S^T q, u = beta (v - g r), o = g p + u (k.q),
+// S <- g S + k u^T, with k.q given per token (aux rows).
+// A column of S belongs to LK = 8 neighbouring lanes, lane j of them keeping rows j R .. j R + R - 1 in registers
+// (R >= d / 8, rows beyond d are zero and stay zero); a warp has 4 columns, a CTA `cb` columns of one (segment, head).
+// Column sums are added within a lane in four chains and across the 8 lanes by shuffles, in an order that depends on
+// (d, dv) only; tokens are staged `chunk` at a time in shared memory, and no thread waits for another CTA.
+// q and k of head h are those of head h / heads_per_qk (MODE 1: several value heads share a (q, k) head).
+// Inputs are float rows: q, k, v in `rows` (ld); MODE 0: decay in `aux` at aux_col + h d; MODE 1: g at aux_col + h,
+// beta at aux_col + H + h, k.q at aux_col + 2 H + h / heads_per_qk. raw_out [tokens, H, dv] float.
+constexpr int LK = 8;
+
+template <int R, int MODE>
+__global__ void __launch_bounds__(256)
+state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_col, int v_col,
+                  const float* __restrict__ aux, int64_t lda, int aux_col, float* __restrict__ state,
+                  const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ raw_out,
+                  int n_heads, int heads_per_qk, int d, int dv, int cb, int chunk, int write_state) {
+    ib::pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DP = LK * R;
+    float* qs = sm;                          // [chunk][DP]
+    float* ks = qs + chunk * DP;             // [chunk][DP]
+    float* as = ks + chunk * DP;             // MODE 0: [chunk][DP] decays; MODE 1: [chunk][4] g, beta, k.q
+    float* vs = as + chunk * (MODE == 0 ? DP : 4);   // [chunk][cb]
+    const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int hq = h / heads_per_qk;
+    const int lk = tid & (LK - 1), col_l = tid >> 3;
+    const int col = blockIdx.z * cb + col_l;
+    const bool live = col < dv;
+    const int k0 = lk * R;
+    const int64_t t0 = seg_start[s];
+    const int len = int(seg_start[s + 1] - t0);
+    float* S_g = state + (int64_t(seg_slot[s]) * n_heads + h) * int64_t(d) * dv;
+    float S[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) S[i] = (live && k0 + i < d) ? S_g[int64_t(k0 + i) * dv + col] : 0.0f;
+
+    for (int c0 = 0; c0 < len; c0 += chunk) {
+        const int n = min(chunk, len - c0);
+        __syncthreads();                     // the last chunk's values have been read
+        for (int idx = tid; idx < n * DP; idx += blockDim.x) {
+            const int c = idx / DP, j = idx - c * DP;
+            const float* row = rows + (t0 + c0 + c) * ld;
+            qs[idx] = j < d ? row[q_col + hq * d + j] : 0.0f;
+            ks[idx] = j < d ? row[k_col + hq * d + j] : 0.0f;
+            if (MODE == 0) as[idx] = j < d ? aux[(t0 + c0 + c) * lda + aux_col + h * d + j] : 0.0f;
+        }
+        if (MODE == 1) {
+            for (int c = tid; c < n; c += blockDim.x) {
+                const float* ar = aux + (t0 + c0 + c) * lda + aux_col;
+                as[c * 4 + 0] = ar[h];
+                as[c * 4 + 1] = ar[n_heads + h];
+                as[c * 4 + 2] = ar[2 * n_heads + hq];
+            }
+        }
+        for (int idx = tid; idx < n * cb; idx += blockDim.x) {
+            const int c = idx / cb, j = blockIdx.z * cb + (idx - c * cb);
+            vs[idx] = j < dv ? rows[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
+        }
+        __syncthreads();
+        for (int c = 0; c < n; c++) {
+            const float v = vs[c * cb + col_l];
+            const float4* q4 = reinterpret_cast<const float4*>(qs + c * DP + k0);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + c * DP + k0);
+            float o;
+            if (MODE == 0) {
+                const float4* a4 = reinterpret_cast<const float4*>(as + c * DP + k0);
+                float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+                for (int i4 = 0; i4 < R / 4; i4++) {
+                    const float4 a = a4[i4], k = k4[i4], q = q4[i4];
+                    S[4 * i4 + 0] = fmaf(a.x, S[4 * i4 + 0], k.x * v);
+                    S[4 * i4 + 1] = fmaf(a.y, S[4 * i4 + 1], k.y * v);
+                    S[4 * i4 + 2] = fmaf(a.z, S[4 * i4 + 2], k.z * v);
+                    S[4 * i4 + 3] = fmaf(a.w, S[4 * i4 + 3], k.w * v);
+                    p0 = fmaf(S[4 * i4 + 0], q.x, p0);
+                    p1 = fmaf(S[4 * i4 + 1], q.y, p1);
+                    p2 = fmaf(S[4 * i4 + 2], q.z, p2);
+                    p3 = fmaf(S[4 * i4 + 3], q.w, p3);
+                }
+                float p = (p0 + p1) + (p2 + p3);
+                p += __shfl_xor_sync(0xffffffffu, p, 1);
+                p += __shfl_xor_sync(0xffffffffu, p, 2);
+                p += __shfl_xor_sync(0xffffffffu, p, 4);
+                o = p;
+            } else {
+                const float g = as[c * 4 + 0], beta = as[c * 4 + 1], kq = as[c * 4 + 2];
+                float r0 = 0.0f, r1 = 0.0f, p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+                for (int i4 = 0; i4 < R / 4; i4++) {
+                    const float4 k = k4[i4], q = q4[i4];
+                    r0 = fmaf(S[4 * i4 + 0], k.x, r0);
+                    r1 = fmaf(S[4 * i4 + 1], k.y, r1);
+                    r0 = fmaf(S[4 * i4 + 2], k.z, r0);
+                    r1 = fmaf(S[4 * i4 + 3], k.w, r1);
+                    p0 = fmaf(S[4 * i4 + 0], q.x, p0);
+                    p1 = fmaf(S[4 * i4 + 1], q.y, p1);
+                    p0 = fmaf(S[4 * i4 + 2], q.z, p0);
+                    p1 = fmaf(S[4 * i4 + 3], q.w, p1);
+                }
+                float r = r0 + r1, p = p0 + p1;
+                r += __shfl_xor_sync(0xffffffffu, r, 1);
+                p += __shfl_xor_sync(0xffffffffu, p, 1);
+                r += __shfl_xor_sync(0xffffffffu, r, 2);
+                p += __shfl_xor_sync(0xffffffffu, p, 2);
+                r += __shfl_xor_sync(0xffffffffu, r, 4);
+                p += __shfl_xor_sync(0xffffffffu, p, 4);
+                const float u = beta * (v - g * r);
+                o = fmaf(u, kq, g * p);
+#pragma unroll
+                for (int i4 = 0; i4 < R / 4; i4++) {
+                    const float4 k = k4[i4];
+                    S[4 * i4 + 0] = fmaf(k.x, u, g * S[4 * i4 + 0]);
+                    S[4 * i4 + 1] = fmaf(k.y, u, g * S[4 * i4 + 1]);
+                    S[4 * i4 + 2] = fmaf(k.z, u, g * S[4 * i4 + 2]);
+                    S[4 * i4 + 3] = fmaf(k.w, u, g * S[4 * i4 + 3]);
+                }
+            }
+            if (lk == 0 && live) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + col] = o;
+        }
+    }
+    if (write_state && live) {
+#pragma unroll
+        for (int i = 0; i < R; i++)
+            if (k0 + i < d) S_g[int64_t(k0 + i) * dv + col] = S[i];
+    }
+}
+
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w [* silu(gate)], lanes striding over the columns; the
+// gate's logits are columns gate_col + h dv + j of rows `gate` (leading dimension ldg).
+template <typename TG, typename TOut>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                      const TG* __restrict__ gate, int64_t ldg, int gate_col, TOut* __restrict__ out,
+                                      int64_t n_rows, int n_heads, int dv) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int64_t t = r / n_heads;
+    const int h = int(r - t * n_heads);
+    const float* x = o + r * dv;
+    float ss = 0.0f;
+    for (int j = lane; j < dv; j += 32) ss = fmaf(x[j], x[j], ss);
+    ss = ib::warp_sum(ss);
+    const float f = 1.0f / sqrtf(ss / float(dv) + eps);
+    for (int j = lane; j < dv; j += 32) {
+        float y = x[j] * f * w[j];
+        if (gate) y *= silu_(ib::to_f32(gate[t * ldg + gate_col + h * dv + j]));
+        out[r * dv + j] = ib::from_f32<TOut>(y);
+    }
+}
+
+}  // namespace
+
+// ================================================================================================
+// C entry points. dtype arguments: 0 = float, 1 = bfloat16.
+
+IB_EXPORT int ib_norm_add(const float* x, const float* y, const float* w, float eps, float* out, void* copy, int copy_dtype,
+                          int64_t n_tokens, int64_t width, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0) return IB_OK;
+    if (!y || !w || !out) return ib::fail(IB_ERR_ARG, "ib_norm_add: rows, weight and result are needed");
+    if (copy && copy_dtype == IB_BF16)
+        IB_LAUNCH(norm_add_kernel<bf16>, unsigned(n_tokens), 256, 0, x, y, w, eps, out, (bf16*)copy, width);
+    else if (!copy || copy_dtype == IB_F32)
+        IB_LAUNCH(norm_add_kernel<float>, unsigned(n_tokens), 256, 0, x, y, w, eps, out, (float*)copy, width);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_norm_add: unknown dtype %d", copy_dtype);
+    return ib::check_launch("ib_norm_add");
+}
+
+IB_EXPORT int ib_cast_rows(const float* x, void* out, int dtype, int64_t n, cudaStream_t stream) {
+    if (n <= 0) return IB_OK;
+    if (dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "ib_cast_rows: unknown dtype %d", dtype);
+    IB_LAUNCH(cast_rows_kernel<bf16>, blocks_for(n, 256), 256, 0, x, (bf16*)out, n);
+    return ib::check_launch("ib_cast_rows");
+}
+
+IB_EXPORT int ib_dual_norm_sum(const float* a, const float* wa, float sa, const float* b, const float* wb, float sb, float eps,
+                               const float* x, const float* wo, float eps_o, float* out, void* copy, int copy_dtype,
+                               int64_t n_tokens, int64_t width, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0) return IB_OK;
+    if (!a || !b || !wa || !wb || !out) return ib::fail(IB_ERR_ARG, "ib_dual_norm_sum: two terms with their weights are needed");
+    const size_t smem = size_t(width) * sizeof(float);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_dual_norm_sum: rows of %lld floats do not fit", (long long)width);
+    if (copy && copy_dtype == IB_BF16)
+        IB_LAUNCH(dual_norm_sum_kernel<bf16>, unsigned(n_tokens), 256, smem, a, wa, sa, b, wb, sb, eps, x, wo, eps_o, out, (bf16*)copy, width);
+    else if (!copy || copy_dtype == IB_F32)
+        IB_LAUNCH(dual_norm_sum_kernel<float>, unsigned(n_tokens), 256, smem, a, wa, sa, b, wb, sb, eps, x, wo, eps_o, out, (float*)copy, width);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_dual_norm_sum: unknown dtype %d", copy_dtype);
+    return ib::check_launch("ib_dual_norm_sum");
+}
+
+IB_EXPORT int ib_glu_act(const void* rows, int64_t ld, int64_t gate_col, int64_t up_col, int64_t width, int kind, float limit,
+                         float limit2, float slope, const float* scale, int64_t group, int64_t n_groups, void* out,
+                         int64_t n_tokens, int dtype, cudaStream_t stream) {
+    const int64_t n = n_tokens * width;
+    if (n <= 0) return IB_OK;
+    if (kind != 0 && kind != 1) return ib::fail(IB_ERR_ARG, "ib_glu_act: unknown activation %d", kind);
+    if (dtype == IB_F32)
+        IB_LAUNCH(glu_act_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)rows, ld, gate_col, up_col, width, kind, limit,
+                  limit2, slope, scale, group, n_groups, (float*)out, n);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(glu_act_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)rows, ld, gate_col, up_col, width, kind, limit,
+                  limit2, slope, scale, group, n_groups, (bf16*)out, n);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_glu_act: unknown dtype %d", dtype);
+    return ib::check_launch("ib_glu_act");
+}
+
+IB_EXPORT int ib_route(const float* logits, int64_t n_tokens, int n_experts, int top, int n_groups, int keep, float sum_eps,
+                       float* weights, int* chosen, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_experts <= 0 || n_groups <= 0 || n_experts % n_groups || keep <= 0 || keep > n_groups || top <= 0 ||
+        top > keep * (n_experts / n_groups))
+        return ib::fail(IB_ERR_ARG, "ib_route: %d experts in %d groups, %d kept, %d chosen", n_experts, n_groups, keep, top);
+    const size_t smem = size_t(4) * (n_experts + n_groups) * sizeof(float);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_route: %d experts do not fit", n_experts);
+    IB_LAUNCH(route_kernel, blocks_for(n_tokens, 4), 128, smem, logits, n_tokens, n_experts, top, n_groups, keep, sum_eps, weights, chosen);
+    return ib::check_launch("ib_route");
+}
+
+IB_EXPORT int ib_rownorm_store(const void* rows, int64_t ld, int col0, const float* wq, const float* wk, float eps,
+                               const int* positions, const int* token_seg, const int* block_table, int64_t max_blocks,
+                               void* q_out, void* k_cache, void* v_cache, int64_t n_tokens, int n_heads, int n_kv, int d, int dv,
+                               int page_size, int write_cache, int64_t n_pages, int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_heads <= 0 || n_kv <= 0 || d <= 0 || dv <= 0 || page_size <= 0) return ib::fail(IB_ERR_ARG, "ib_rownorm_store: bad sizes");
+    if (dtype == IB_F32)
+        IB_LAUNCH(rownorm_store_kernel<float>, unsigned(n_tokens), 256, 0, (const float*)rows, ld, col0, wq, wk, eps, positions, token_seg,
+                  block_table, max_blocks, (float*)q_out, (float*)k_cache, (float*)v_cache, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(rownorm_store_kernel<bf16>, unsigned(n_tokens), 256, 0, (const bf16*)rows, ld, col0, wq, wk, eps, positions, token_seg,
+                  block_table, max_blocks, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, n_heads, n_kv, d, dv, page_size, write_cache, n_pages, status);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_rownorm_store: unknown dtype %d", dtype);
+    return ib::check_launch("ib_rownorm_store");
+}
+
+IB_EXPORT int ib_decay_gates(float* rows, int64_t ld, int q_col, int low_col, int rank, const float* up, const float* bias,
+                             float tau, float q_scale, float* decay, int64_t n_tokens, int channels, cudaStream_t stream) {
+    if (n_tokens <= 0 || channels <= 0) return IB_OK;
+    if (rank <= 0 || !(tau > 0.0f)) return ib::fail(IB_ERR_ARG, "ib_decay_gates: rank %d, tau %f", rank, double(tau));
+    IB_LAUNCH(decay_gates_kernel, blocks_for(n_tokens * channels, 256), 256, 0, rows, ld, q_col, low_col, rank, up, bias, 1.0f / tau,
+              q_scale, decay, n_tokens, channels);
+    return ib::check_launch("ib_decay_gates");
+}
+
+// The widest (q, k) head that ib_delta_prepare takes.
+IB_EXPORT int ib_delta_prepare_max_dim() { return 32 * PREP_PER_LANE; }
+
+IB_EXPORT int ib_delta_prepare(const float* rows, int64_t ld, int col0, int a_col, int b_col, const float* filt_w, int taps,
+                               const float* tails, const float* a_log, const float* dt_bias, float unit_eps, float q_scale,
+                               const int* token_seg, const int* seg_start, const int* seg_slot, float* prep, int64_t ldp,
+                               int64_t n_tokens, int n_heads, int n_qk, int d, int dv, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_heads <= 0 || n_qk <= 0 || n_heads % n_qk || d <= 0 || dv <= 0 || d > 32 * PREP_PER_LANE)
+        return ib::fail(IB_ERR_ARG, "ib_delta_prepare: %d heads on %d (q, k) heads of %d, values of %d", n_heads, n_qk, d, dv);
+    if (filt_w && taps > 1 && !tails) return ib::fail(IB_ERR_ARG, "ib_delta_prepare: a filter of %d taps needs tails", taps);
+    if (ldp < 2 * int64_t(n_qk) * d + int64_t(n_heads) * dv + 2 * n_heads + n_qk) return ib::fail(IB_ERR_ARG, "ib_delta_prepare: prepared rows too short");
+    const int64_t warps = n_tokens * (n_qk + n_heads + 1);
+    IB_LAUNCH(delta_prepare_kernel, blocks_for(warps, 4), 128, 0, rows, ld, col0, a_col, b_col, filt_w, filt_w ? taps : 0, tails, a_log,
+              dt_bias, unit_eps, q_scale, token_seg, seg_start, seg_slot, prep, ldp, n_tokens, n_heads, n_qk, d, dv);
+    return ib::check_launch("ib_delta_prepare");
+}
+
+IB_EXPORT int ib_tail_update(const float* rows, int64_t ld, int col0, int channels, int taps, float* tails, const int* seg_start,
+                             const int* seg_slot, int n_segments, cudaStream_t stream) {
+    if (n_segments <= 0 || channels <= 0 || taps <= 1) return IB_OK;
+    if (n_segments > 65535) return ib::fail(IB_ERR_ARG, "ib_tail_update: too many segments");
+    const dim3 grid{blocks_for(channels, 128), unsigned(n_segments), 1u};
+    IB_LAUNCH(tail_update_kernel, grid, 128, 0, rows, ld, col0, channels, taps, tails, seg_start, seg_slot);
+    return ib::check_launch("ib_tail_update");
+}
+
+// The largest key size a head of ib_state_scan may have.
+IB_EXPORT int ib_state_scan_max_dim() { return LK * 32; }
+
+template <int R, int MODE>
+static int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* rows, int64_t ld, int q_col,
+                       int k_col, int v_col, const float* aux, int64_t lda, int aux_col, float* state, const int* seg_start,
+                       const int* seg_slot, float* raw_out, int n_heads, int hpq, int d, int dv, int cb, int chunk, int write_state) {
+    IB_LAUNCH((state_scan_kernel<R, MODE>), grid, threads, smem, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start,
+              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state);
+    return ib::check_launch("ib_state_scan");
+}
+
+// mode 0: a decay per key channel (aux: decays at aux_col + h d); mode 1: gated delta rule (aux: g, beta, k.q).
+// `spread` (prompt portions): a head's columns go to more, smaller CTAs until there is about one per SM (sm_count).
+IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, int k_col, int v_col, const float* aux,
+                            int64_t lda, int aux_col, float* state, const int* seg_start, const int* seg_slot,
+                            float* raw_out, int n_segments, int n_heads, int heads_per_qk, int d, int dv, int write_state,
+                            int spread, int sm_count, cudaStream_t stream) {
+    if (n_segments <= 0) return IB_OK;
+    if (n_heads <= 0 || n_heads > 65535 || heads_per_qk <= 0 || n_heads % heads_per_qk || d <= 0 || dv <= 0 || d > LK * 32)
+        return ib::fail(IB_ERR_ARG, "ib_state_scan: %d heads with a state of %d x %d do not fit", n_heads, d, dv);
+    if (mode != 0 && mode != 1) return ib::fail(IB_ERR_ARG, "ib_state_scan: unknown mode %d", mode);
+    const int r = d <= 32 ? 4 : (d <= 64 ? 8 : (d <= 128 ? 16 : 32));
+    int cb = 32;
+    while (cb > 4 && cb / 2 >= dv) cb /= 2;                     // no CTA wider than the head
+    if (spread) {
+        const int sms = sm_count > 0 ? sm_count : 148;
+        while (cb > 8 && n_segments * n_heads * ((dv + cb / 2 - 1) / (cb / 2)) <= sms) cb /= 2;
+    }
+    const int dp = LK * r;
+    const int per_token = 2 * dp + (mode == 0 ? dp : 4) + cb;
+    int chunk = 11264 / per_token;
+    chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
+    const size_t smem = size_t(chunk) * per_token * sizeof(float);
+    const dim3 grid{unsigned(n_segments), unsigned(n_heads), unsigned((dv + cb - 1) / cb)};
+    const int threads = cb * LK;
+#define IB_SCAN(RR, MM)                                                                                                          \
+    return launch_scan<RR, MM>(grid, threads, smem, stream, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start, \
+                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state)
+    if (mode == 0) {
+        if (r == 4) IB_SCAN(4, 0);
+        if (r == 8) IB_SCAN(8, 0);
+        if (r == 16) IB_SCAN(16, 0);
+        IB_SCAN(32, 0);
+    }
+    if (r == 4) IB_SCAN(4, 1);
+    if (r == 8) IB_SCAN(8, 1);
+    if (r == 16) IB_SCAN(16, 1);
+    IB_SCAN(32, 1);
+#undef IB_SCAN
+}
+
+IB_EXPORT int ib_head_norm_gate(const float* o, const float* w, float eps, const void* gate, int64_t ldg, int gate_col,
+                                int gate_dtype, void* out, int out_dtype, int64_t n_tokens, int n_heads, int dv,
+                                cudaStream_t stream) {
+    const int64_t rows = n_tokens * n_heads;
+    if (rows <= 0 || dv <= 0) return IB_OK;
+    const unsigned grid = blocks_for(rows, 8);
+#define IB_HN(TG, TO) IB_LAUNCH((head_norm_gate_kernel<TG, TO>), grid, 256, 0, o, w, eps, (const TG*)gate, ldg, gate_col, (TO*)out, rows, n_heads, dv)
+    if (!gate || gate_dtype == IB_F32) {
+        if (out_dtype == IB_F32) IB_HN(float, float);
+        else if (out_dtype == IB_BF16) IB_HN(float, bf16);
+        else return ib::fail(IB_ERR_ARG, "ib_head_norm_gate: unknown dtype %d", out_dtype);
+    } else if (gate_dtype == IB_BF16) {
+        if (out_dtype == IB_F32) IB_HN(bf16, float);
+        else if (out_dtype == IB_BF16) IB_HN(bf16, bf16);
+        else return ib::fail(IB_ERR_ARG, "ib_head_norm_gate: unknown dtype %d", out_dtype);
+    } else {
+        return ib::fail(IB_ERR_ARG, "ib_head_norm_gate: unknown gate dtype %d", gate_dtype);
+    }
+#undef IB_HN
+    return ib::check_launch("ib_head_norm_gate");
+}

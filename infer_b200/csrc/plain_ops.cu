@@ -314,6 +314,8 @@ rope_kv_write_vec_kernel(const bf16* __restrict__ qkv, const float* __restrict__
 // aligned to absolute multiples of 128, softmax is computed online over the tiles, so the result
 // depends on (lo, p) only. Values may have another size than keys (v_dim; the value pages are
 // [kv_heads, page_size, v_dim] then), and the output rows are [heads, v_dim].
+// Optional: a learned bias per (distance, head), dist_bias[min(p - j, bias_len - 1) * heads + h], added to the scaled
+// score; and a sink per head, a logit without key or value that only enters the softmax denominator, once.
 constexpr int AT = 128;
 
 template <typename T>
@@ -321,7 +323,8 @@ __global__ void __launch_bounds__(AT)
 attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                  const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
                  const int* __restrict__ positions, T* __restrict__ out, int n_heads, int n_kv, int head_dim, int v_dim,
-                 int page_size, int window, float scale, int64_t n_pages, int* status) {
+                 int page_size, int window, float scale, int64_t n_pages, int* status,
+                 const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ sink) {
     ib::pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                      // [head_dim], rounded up to an even count: the 8-byte rows behind stay aligned
@@ -339,6 +342,10 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 
     for (int d = tid; d < head_dim; d += AT) qs[d] = ib::to_f32(q[(t * n_heads + h) * head_dim + d]);
     float m = -INFINITY, l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+    if (sink) {                            // the running maximum starts at the sink's logit, the sum at exp(0)
+        m = sink[h];
+        l = 1.0f;
+    }
     __syncthreads();
 
     for (int tile = (lo / AT) * AT; tile <= pos; tile += AT) {
@@ -357,6 +364,7 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                 float dot = 0.0f;
                 for (int d = 0; d < head_dim; d++) dot = fmaf(qs[d], ib::to_f32(kr[d]), dot);
                 s = dot * scale;
+                if (dist_bias) s += dist_bias[int64_t(min(pos - j, bias_len - 1)) * n_heads + h];
             }
         }
         const float tile_max = ib::block_max(s, red);
@@ -691,8 +699,10 @@ IB_EXPORT int ib_attention_plain_max_head_dim() { return 2 * AT; }
 IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                  int64_t max_blocks, const int* token_seg, const int* positions, void* out,
                                  int64_t n_tokens, int n_heads, int n_kv, int head_dim, int page_size, int window,
-                                 float scale, int64_t n_pages, int dtype, int* status, cudaStream_t stream, int v_dim) {
+                                 float scale, int64_t n_pages, int dtype, int* status, cudaStream_t stream, int v_dim,
+                                 const float* dist_bias, int bias_len, const float* sink) {
     if (n_tokens <= 0) return IB_OK;
+    if (dist_bias && bias_len <= 0) return ib::fail(IB_ERR_ARG, "ib_attention_plain: a distance bias needs at least one row");
     if (v_dim <= 0) v_dim = head_dim;                       // values as long as keys
     if (head_dim <= 0 || head_dim > 2 * AT || v_dim > 2 * AT)
         return ib::fail(IB_ERR_ARG, "ib_attention_plain: head sizes %d / %d are outside 1..%d", head_dim, v_dim, 2 * AT);
@@ -702,10 +712,12 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
     const size_t smem = size_t(((head_dim + 1) & ~1) + AT) * sizeof(float) + AT * sizeof(int64_t) + 8;
     if (dtype == IB_F32)
         IB_LAUNCH(attention_kernel<float>, grid, AT, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache,
-            block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status);
+            block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status,
+            dist_bias, bias_len, sink);
     else if (dtype == IB_BF16)
         IB_LAUNCH(attention_kernel<bf16>, grid, AT, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-            block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status);
+            block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status,
+            dist_bias, bias_len, sink);
     else
         return ib::fail(IB_ERR_ARG, "ib_attention_plain: unknown dtype %d", dtype);
     return ib::check_launch("ib_attention_plain");

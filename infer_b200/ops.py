@@ -188,9 +188,12 @@ def rope_kv_write(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                     token_seg: torch.Tensor, positions: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                     window: Optional[int], scale: float, status: Optional[torch.Tensor] = None,
-                    v_head_dim: Optional[int] = None) -> torch.Tensor:
+                    v_head_dim: Optional[int] = None, dist_bias: Optional[torch.Tensor] = None,
+                    sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every token over its request's pages; returns [T, heads*v_head_dim] (values are as long
-    as keys unless ``v_head_dim`` says otherwise; the value pages are [pages, kv_heads, page_size, v_head_dim])."""
+    as keys unless ``v_head_dim`` says otherwise; the value pages are [pages, kv_heads, page_size, v_head_dim]).
+    ``dist_bias`` float32 [L, heads]: row min(distance, L - 1) is added to the scaled scores of a query's keys;
+    ``sink`` float32 [heads]: a logit per head that enters the softmax denominator only."""
     _check(q, "q")
     T = q.shape[0]
     vd = int(v_head_dim or head_dim)
@@ -204,11 +207,18 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     _check(token_seg, "token_seg", torch.int32, (T,))
     _check(block_table, "block_table", torch.int32)
     out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
+    if dist_bias is not None:
+        _check(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != n_heads:
+            raise KernelError(f"dist_bias must be [distances, {n_heads}], got {tuple(dist_bias.shape)}")
+    if sink is not None:
+        _check(sink, "sink", torch.float32, (n_heads,))
     f = _fn("plain", "ib_attention_plain", [c_void_p] * 4 + [c_int64] + [c_void_p] * 3 + [c_int64] + [c_int] * 5 +
-            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int])
+            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p])
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           token_seg.data_ptr(), positions.data_ptr(), out.data_ptr(), T, n_heads, n_kv, head_dim, page_size,
-          int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream(), vd)
+          int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream(), vd,
+          _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink))
     return out
 
 
@@ -441,4 +451,270 @@ def gated_recurrence(proj: torch.Tensor, q_col: int, f_col: int, v_col: int, low
     _call(f, proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col), lower.data_ptr(), norm_weight.data_ptr(), float(eps),
           state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, dim, v_dim,
           int(write_state), dtype_code(out_dtype), _stream(), int(spread), _ptr(scratch), T, sm_count, RECURRENCE_COLUMN_BLOCK)
+    return out
+
+
+# ----------------------------------------------------------------------------- norms on sublayer results, routed
+# feed-forwards, whole-row q/k norms, recurrences with a decay per key channel and with the delta rule
+
+def norm_add(x: Optional[torch.Tensor], y: torch.Tensor, weight: torch.Tensor, eps: float,
+             copy_dtype: Optional[torch.dtype] = None):
+    """x + y / sqrt(mean(y^2) + eps) * weight per row, float32 [T, W], written over x (x None: the norm alone, a new
+    tensor). With ``copy_dtype`` also the same rows in that dtype (for a matrix product that reads them); returns
+    (rows, copy or None)."""
+    _check(y, "y", torch.float32)
+    T, W = y.shape
+    _check(weight, "weight", torch.float32, (W,))
+    if x is not None:
+        _check(x, "x", torch.float32, (T, W))
+    out = x if x is not None else torch.empty_like(y)
+    copy = None
+    if copy_dtype is not None and copy_dtype != torch.float32:
+        copy = torch.empty((T, W), dtype=copy_dtype, device=y.device)
+    f = _fn("mix", "ib_norm_add", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p])
+    _call(f, _ptr(x), y.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(), _ptr(copy),
+          dtype_code(copy.dtype) if copy is not None else 0, T, W, _stream())
+    return out, copy
+
+
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """float32 rows in ``dtype`` (x itself for float32)."""
+    _check(x, "x", torch.float32)
+    if dtype == torch.float32:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    f = _fn("mix", "ib_cast_rows", [c_void_p, c_void_p, c_int, c_int64, c_void_p])
+    _call(f, x.data_ptr(), out.data_ptr(), dtype_code(dtype), x.numel(), _stream())
+    return out
+
+
+def dual_norm_sum(a: torch.Tensor, wa: torch.Tensor, sa: float, b: torch.Tensor, wb: torch.Tensor, sb: float, eps: float,
+                  x: Optional[torch.Tensor] = None, wo: Optional[torch.Tensor] = None, eps_o: float = 0.0,
+                  copy_dtype: Optional[torch.dtype] = None):
+    """m = sa * a / rms(a) * wa + sb * b / rms(b) * wb per row (float32 [T, W]). Without ``wo`` returns (m, None).
+    With ``wo``: x + m / rms(m) * wo, written over x (x None: a new tensor), and its copy in ``copy_dtype`` if given:
+    returns (rows, copy or None)."""
+    _check(a, "a", torch.float32)
+    T, W = a.shape
+    _check(b, "b", torch.float32, (T, W))
+    _check(wa, "wa", torch.float32, (W,))
+    _check(wb, "wb", torch.float32, (W,))
+    if wo is not None:
+        _check(wo, "wo", torch.float32, (W,))
+    if x is not None:
+        _check(x, "x", torch.float32, (T, W))
+    out = x if (x is not None and wo is not None) else torch.empty_like(a)
+    copy = None
+    if wo is not None and copy_dtype is not None and copy_dtype != torch.float32:
+        copy = torch.empty((T, W), dtype=copy_dtype, device=a.device)
+    f = _fn("mix", "ib_dual_norm_sum", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+                                        c_float, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p])
+    _call(f, a.data_ptr(), wa.data_ptr(), float(sa), b.data_ptr(), wb.data_ptr(), float(sb), float(eps),
+          _ptr(x) if wo is not None else None, _ptr(wo), float(eps_o), out.data_ptr(), _ptr(copy),
+          dtype_code(copy.dtype) if copy is not None else 0, T, W, _stream())
+    return out, copy
+
+
+GLU_KINDS = {"gelu_tanh": 0, "clipped_swish": 1}
+
+
+def glu_act(rows: torch.Tensor, gate_col: int, up_col: int, width: int, kind: str, limit: float = 0.0,
+            limit2: float = 0.0, slope: float = 1.0, scale: Optional[torch.Tensor] = None, group: int = 0,
+            n_groups: int = 0) -> torch.Tensor:
+    """The hidden layer of a gated feed-forward, from rows [T, ld] that hold gate and up columns -> [T, width].
+    "gelu_tanh": gelu_tanh(g) * u. "clipped_swish": g' = min(g, limit), u' = clamp(u, -limit, limit),
+    g' * sigmoid(slope * g') * (u' + 1). With ``scale`` float32 [T, n_groups]: block e of ``group`` columns is
+    multiplied by scale[t, e]; columns from n_groups * group on are not scaled and use ``limit2``."""
+    _check(rows, "rows")
+    T, ld = rows.shape
+    if min(gate_col, up_col) < 0 or max(gate_col, up_col) + width > ld:
+        raise KernelError("the gate or up columns lie outside the rows")
+    if scale is not None:
+        _check(scale, "scale", torch.float32, (T, n_groups))
+    out = torch.empty((T, width), dtype=rows.dtype, device=rows.device)
+    f = _fn("mix", "ib_glu_act", [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_float, c_float, c_void_p,
+                                  c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(gate_col), int(up_col), int(width), GLU_KINDS[kind], float(limit), float(limit2),
+          float(slope), _ptr(scale), int(group), int(n_groups), out.data_ptr(), T, dtype_code(rows.dtype), _stream())
+    return out
+
+
+def route(logits: torch.Tensor, top: int, n_groups: int = 1, keep: int = 1, sum_eps: float = 0.0, want_chosen: bool = False):
+    """Router of a mixture of experts on float32 logits [T, E]: softmax over all experts; the ``keep`` groups (of
+    E / n_groups neighbouring experts) with the largest single score stay; of their experts the ``top`` largest are
+    chosen; weights are scores / (their sum + sum_eps). Returns (weights float32 [T, E], zero where not chosen;
+    chosen int32 [T, top] or None)."""
+    _check(logits, "logits", torch.float32)
+    T, E = logits.shape
+    weights = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device) if want_chosen else None
+    f = _fn("mix", "ib_route", [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
+    _call(f, logits.data_ptr(), T, E, int(top), int(n_groups), int(keep), float(sum_eps), weights.data_ptr(), _ptr(chosen), _stream())
+    return weights, chosen
+
+
+def rownorm_store(rows: torch.Tensor, col0: int, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float, step,
+                  block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_heads: int, n_kv: int,
+                  head_dim: int, v_head_dim: int, write_cache: bool = True) -> torch.Tensor:
+    """Projected rows [.. | q | k | v | ..] (q at column col0) -> q [T, heads * head_dim] with ALL of a token's q
+    channels divided by their root mean square and multiplied by wq [heads * head_dim] (k likewise with wk, into the
+    token's page; v into its page as it is)."""
+    _check(rows, "rows")
+    T, ld = rows.shape
+    nq, nk, nv = n_heads * head_dim, n_kv * head_dim, n_kv * v_head_dim
+    if ld < col0 + nq + nk + nv:
+        raise KernelError("q, k and v lie outside the rows")
+    n_pages, ckv, page_size, chd = k_cache.shape
+    _check(k_cache, "k_cache", rows.dtype, (n_pages, n_kv, page_size, head_dim))
+    _check(v_cache, "v_cache", rows.dtype, (n_pages, n_kv, page_size, v_head_dim))
+    if wq is not None:
+        _check(wq, "wq", torch.float32, (nq,))
+    if wk is not None:
+        _check(wk, "wk", torch.float32, (nk,))
+    _check(block_table, "block_table", torch.int32)
+    q = torch.empty((T, nq), dtype=rows.dtype, device=rows.device)
+    f = _fn("mix", "ib_rownorm_store", [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                        c_void_p, c_void_p, c_void_p, c_int64] + [c_int] * 6 + [c_int64, c_int, c_void_p, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(col0), _ptr(wq), _ptr(wk), float(eps), step.positions.data_ptr(), step.token_seg.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T, n_heads, n_kv,
+          head_dim, v_head_dim, page_size, int(write_cache), n_pages, dtype_code(rows.dtype), _ptr(step.status), _stream())
+    return q
+
+
+def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
+                     dist_bias, sink):
+    """A faster kernel for attention with a distance bias and a sink where it takes the shape; None where it does not
+    (the caller then uses the plain kernel)."""
+    return None
+
+
+def decay_gates(rows: torch.Tensor, q_col: int, low_col: int, rank: int, up: torch.Tensor, bias: Optional[torch.Tensor],
+                tau: float, q_scale: float) -> torch.Tensor:
+    """decay[t, c] = sigmoid(bias[c] + up[c, :] . rows[t, low_col : low_col + rank]) ^ (1 / tau), float32 [T, C] with
+    C = up.shape[0]; also multiplies columns [q_col, q_col + C) of the float32 rows by q_scale, in place."""
+    _check(rows, "rows", torch.float32)
+    T, ld = rows.shape
+    _check(up, "up", torch.float32)
+    C = up.shape[0]
+    if up.shape[1] != rank or low_col + rank > ld or q_col + C > ld:
+        raise KernelError("decay_gates: the low-rank columns or q lie outside the rows")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, (C,))
+    decay = torch.empty((T, C), dtype=torch.float32, device=rows.device)
+    f = _fn("mix", "ib_decay_gates", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                                      c_int64, c_int, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(q_col), int(low_col), int(rank), up.data_ptr(), _ptr(bias), float(tau), float(q_scale),
+          decay.data_ptr(), T, C, _stream())
+    return decay
+
+
+def delta_prepare_max_dim() -> int:
+    return int(_fn("mix", "ib_delta_prepare_max_dim", [])())
+
+
+def state_scan_max_dim() -> int:
+    return int(_fn("mix", "ib_state_scan_max_dim", [])())
+
+
+def delta_prepare(rows: torch.Tensor, col0: int, a_col: int, b_col: int, filt_w: Optional[torch.Tensor],
+                  tails: Optional[torch.Tensor], a_log: torch.Tensor, dt_bias: torch.Tensor, unit_eps: float, q_scale: float,
+                  step, n_heads: int, n_qk: int, dim: int, v_dim: int) -> torch.Tensor:
+    """What the gated delta rule reads, from float32 projected rows [.. q (n_qk x dim) | k | v (n_heads x v_dim) ..]
+    (from column col0; per-head step-size logits at a_col, write-strength logits at b_col): every q, k, v channel
+    through its causal filter (``filt_w`` float32 [taps, channels], ``tails`` float32 [slots, taps - 1, channels]) and
+    silu; q and k made unit vectors per head, q times q_scale. Returns float32 [T, q | k | v | g | beta | k.q]."""
+    _check(rows, "rows", torch.float32)
+    T, ld = rows.shape
+    C = 2 * n_qk * dim + n_heads * v_dim
+    if col0 + C > ld or a_col + n_heads > ld or b_col + n_heads > ld:
+        raise KernelError("delta_prepare: columns lie outside the rows")
+    taps = 0
+    if filt_w is not None:
+        _check(filt_w, "filt_w", torch.float32)
+        if filt_w.shape[1] != C:
+            raise KernelError(f"the filter has {filt_w.shape[1]} channels, the rows {C}")
+        taps = filt_w.shape[0]
+        if taps > 1:
+            _check(tails, "tails", torch.float32)
+            if tuple(tails.shape[1:]) != (taps - 1, C):
+                raise KernelError(f"tails must be [slots, {taps - 1}, {C}], got {tuple(tails.shape)}")
+    _check(a_log, "a_log", torch.float32, (n_heads,))
+    _check(dt_bias, "dt_bias", torch.float32, (n_heads,))
+    ldp = (C + 2 * n_heads + n_qk + 3) // 4 * 4
+    prep = torch.empty((T, ldp), dtype=torch.float32, device=rows.device)
+    f = _fn("mix", "ib_delta_prepare", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(col0), int(a_col), int(b_col), _ptr(filt_w), taps, _ptr(tails) if taps > 1 else None,
+          a_log.data_ptr(), dt_bias.data_ptr(), float(unit_eps), float(q_scale), step.token_seg.data_ptr(), step.seg_start.data_ptr(),
+          step.seg_slot.data_ptr(), prep.data_ptr(), ldp, T, n_heads, n_qk, dim, v_dim, _stream())
+    return prep
+
+
+def tail_update(rows: torch.Tensor, col0: int, tails: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor) -> None:
+    """After a step: tails[slot of s] (float32 [slots, taps - 1, C]) becomes the last taps - 1 rows of (old tail,
+    columns [col0, col0 + C) of segment s's float32 rows)."""
+    _check(rows, "rows", torch.float32)
+    _check(tails, "tails", torch.float32)
+    keep, C = tails.shape[1], tails.shape[2]
+    f = _fn("mix", "ib_tail_update", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _call(f, rows.data_ptr(), rows.shape[1], int(col0), C, keep + 1, tails.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(),
+          seg_slot.numel(), _stream())
+
+
+SCAN_ROW_DECAY, SCAN_DELTA_RULE = 0, 1
+SCAN_SPREAD_FROM = 8          # segments of more tokens than this spread a head's columns over more CTAs
+
+
+def state_scan(mode: int, rows: torch.Tensor, q_col: int, k_col: int, v_col: int, aux: torch.Tensor, aux_col: int,
+               state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor, n_heads: int, heads_per_qk: int,
+               dim: int, v_dim: int, write_state: bool = True, max_len: int = 1) -> torch.Tensor:
+    """A linear recurrence with a float32 matrix state [slots, heads, dim, v_dim], over the tokens of every segment
+    in order. SCAN_ROW_DECAY: S <- diag(a) S + k v^T, o = S^T q, with a in ``aux`` columns aux_col + h * dim.
+    SCAN_DELTA_RULE: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with ``aux`` columns [g (heads) | beta
+    (heads) | k.q (heads / heads_per_qk)] from aux_col. q, k at q_col, k_col + (h // heads_per_qk) * dim and v at
+    v_col + h * v_dim of the float32 ``rows``. Returns o float32 [T, heads * v_dim]."""
+    _check(rows, "rows", torch.float32)
+    _check(aux, "aux", torch.float32)
+    _check(state, "state", torch.float32)
+    T, ld = rows.shape
+    if tuple(state.shape[1:]) != (n_heads, dim, v_dim):
+        raise KernelError(f"state must be [slots, {n_heads}, {dim}, {v_dim}], got {tuple(state.shape)}")
+    n_qk = n_heads // heads_per_qk
+    if max(q_col, k_col) + n_qk * dim > ld or v_col + n_heads * v_dim > ld:
+        raise KernelError("the q, k or v columns lie outside the rows")
+    need = n_heads * dim if mode == SCAN_ROW_DECAY else 2 * n_heads + n_qk
+    if aux.shape[0] != T or aux_col + need > aux.shape[1]:
+        raise KernelError("the decay columns lie outside their rows")
+    S = seg_slot.numel()
+    _check(seg_start, "seg_start", torch.int32, (S + 1,))
+    out = torch.empty((T, n_heads * v_dim), dtype=torch.float32, device=rows.device)
+    spread = int(max_len) >= SCAN_SPREAD_FROM
+    sm_count = torch.cuda.get_device_properties(rows.device).multi_processor_count if spread else 0
+    f = _fn("mix", "ib_state_scan", [c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_void_p] + [c_int] * 8 + [c_void_p])
+    _call(f, int(mode), rows.data_ptr(), ld, int(q_col), int(k_col), int(v_col), aux.data_ptr(), aux.shape[1], int(aux_col),
+          state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, int(heads_per_qk), dim, v_dim,
+          int(write_state), int(spread), sm_count, _stream())
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Optional[torch.Tensor], gate_col: int,
+                   n_heads: int, v_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per (token, head): o / sqrt(mean(o^2) + eps) * weight [v_dim], times silu of the gate's logits (columns
+    gate_col + h * v_dim of rows ``gate``, float32 or bfloat16) if given. o float32 [T, heads * v_dim]."""
+    _check(o, "o", torch.float32)
+    T = o.shape[0]
+    _check(o, "o", None, (T, n_heads * v_dim))
+    _check(weight, "weight", torch.float32, (v_dim,))
+    ldg = 0
+    if gate is not None:
+        _check(gate, "gate")
+        ldg = gate.shape[1]
+        if gate.shape[0] != T or gate_col + n_heads * v_dim > ldg:
+            raise KernelError("the gate columns lie outside the rows")
+    out = torch.empty((T, n_heads * v_dim), dtype=out_dtype, device=o.device)
+    f = _fn("mix", "ib_head_norm_gate", [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int64,
+                                         c_int, c_int, c_void_p])
+    _call(f, o.data_ptr(), weight.data_ptr(), float(eps), _ptr(gate), ldg, int(gate_col),
+          dtype_code(gate.dtype) if gate is not None else 0, out.data_ptr(), dtype_code(out_dtype), T, n_heads, v_dim, _stream())
     return out

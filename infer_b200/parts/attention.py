@@ -17,8 +17,15 @@ Options beyond that, each a key of the part's spec (absent = off):
 ``value_norm_eps``  every value head is divided by sqrt(mean(v^2) + eps) before it is cached
 ``head_gate``       head h's context is multiplied by sigmoid(x Wg^T)[h] before the output product; Wg's rows ride
                     in the same matrix product as q, k and v
-``names``           local tensor names by role (q, k, v, o, q_bias, k_bias, v_bias, q_filter, k_filter, v_filter, gate)
-                    for checkpoints that call them otherwise
+``qk_row_norm_eps`` ALL of a token's q channels (every head at once) are divided by their root mean square and
+                    multiplied by a weight per channel (role q_norm, [heads * head_dim]); k likewise (k_norm); no
+                    rotation follows. One kernel normalises and fills the pages
+``distance_bias``   {"buckets": B or None, "max_distance": D}: a learned table (role rel, [B, heads]; B is read from
+                    the tensor when the spec gives None) whose row bucket(i - j) is added to the scaled score of query i
+                    and key j: bucket(n) = n below B // 2, then logarithmic steps that reach the last row at n = D
+``sink``            a learned logit per head (role sink, [heads]) that enters the softmax denominator only
+``names``           local tensor names by role (q, k, v, o, q_bias, k_bias, v_bias, q_filter, k_filter, v_filter, gate,
+                    q_norm, k_norm, rel, sink) for checkpoints that call them otherwise
 """
 from __future__ import annotations
 
@@ -34,11 +41,37 @@ from .linear import Linear
 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
           "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-          "q_filter": "q_proj.filter", "k_filter": "k_proj.filter", "v_filter": "v_proj.filter", "gate": "gate_proj.weight"}
+          "q_filter": "q_proj.filter", "k_filter": "k_proj.filter", "v_filter": "v_proj.filter", "gate": "gate_proj.weight",
+          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "rel": "distance_bias.weight", "sink": "sinks"}
 
 
 def _names(spec: PartSpec):
     return {**_NAMES, **dict(spec.get("names") or {})}
+
+
+def log_bucket(n: int, buckets: int, max_distance: float) -> int:
+    """Row of a distance-bias table of ``buckets`` rows for a distance n >= 0: one row per distance below
+    buckets // 2, then logarithmic steps up to ``max_distance``, where the last row is reached."""
+    half = buckets // 2
+    if n < half:
+        return n
+    return min(buckets - 1, half + int(math.floor(math.log(n / half) / math.log(max_distance / half) * (buckets - half))))
+
+
+def distance_bias_table(rel: torch.Tensor, max_distance: float, window: Optional[int]) -> torch.Tensor:
+    """float32 [L, heads]: row n is the bias of distance n, the last row that of every larger distance (a window
+    bounds the distances that are ever asked for)."""
+    B = rel.shape[0]
+    if B < 2 or not max_distance > B // 2:
+        raise ValueError(f"a distance bias of {B} rows needs max_distance above {B // 2}, got {max_distance}")
+    rows, n = [], 0
+    while True:
+        b = log_bucket(n, B, max_distance)
+        rows.append(b)
+        if b == B - 1 or (window is not None and n + 1 >= window):
+            break
+        n += 1
+    return rel.float()[torch.tensor(rows, dtype=torch.long)].contiguous()
 
 
 @register_mixer("attention")
@@ -80,6 +113,21 @@ class Attention(Mixer):
                                  f"got {self.head_dim} / {self.v_dim}")
             if self.position is not None and getattr(self.position, "layout", None) != "pairs":
                 raise ValueError("filters, value norm, gates and other value sizes go with position kind 'rotary_pairs' (or none)")
+        self.row_norm_eps = spec.get("qk_row_norm_eps")
+        self.distance_bias = spec.get("distance_bias")
+        self.has_sink = bool(spec.get("sink", False))
+        self.row_norm = self.row_norm_eps is not None
+        if self.row_norm or self.distance_bias is not None or self.has_sink:
+            # these scores are not the ones the fast kernels compute; the projected rows go through the row-norm kernel
+            if self.taps > 0 or self.position is not None or self.value_norm_eps is not None or self.head_gate:
+                raise ValueError("row norms, distance bias and sinks do not combine with filters, rotation, value norm or head gates")
+            if self.row_norm and float(self.row_norm_eps) <= 0:
+                raise ValueError("qk_row_norm_eps must be positive")
+            self.prepared = False
+            self.biased = True
+        else:
+            self.biased = False
+        self.q_norm_w = self.k_norm_w = self.bias_table = self.sink_w = None
         self.n_qkv = (self.n_heads + self.n_kv) * self.head_dim + self.n_kv * self.v_dim
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
@@ -98,6 +146,13 @@ class Attention(Mixer):
             shapes.update({n["q_filter"]: (nh * hd, taps), n["k_filter"]: (nkv * hd, taps), n["v_filter"]: (nkv * vd, taps)})
         if spec.get("head_gate", False):
             shapes[n["gate"]] = (nh, H)
+        if spec.get("qk_row_norm_eps") is not None:
+            shapes.update({n["q_norm"]: (nh * hd,), n["k_norm"]: (nkv * hd,)})
+        db = spec.get("distance_bias")
+        if db is not None:
+            shapes[n["rel"]] = (int(db["buckets"]) if db.get("buckets") is not None else -1, nh)
+        if spec.get("sink", False):
+            shapes[n["sink"]] = (nh,)
         return shapes
 
     @classmethod
@@ -108,6 +163,10 @@ class Attention(Mixer):
             w = 0.3 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
             w[:, -1] += 1.0
             return w
+        if name in (n["q_norm"], n["k_norm"]):
+            return 1.0 + 0.1 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
+        if name in (n["rel"], n["sink"]):
+            return torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
         return super().init_params(spec, name, shape, gen)
 
     def load(self, params):
@@ -126,6 +185,13 @@ class Attention(Mixer):
                 b = torch.cat([b, torch.zeros(w.shape[0] - b.numel(), device=b.device)])
         self.qkv = Linear(self.rt, w, b)
         self.o = Linear(self.rt, params[n["o"]])
+        f32 = dict(device=self.rt.device, dtype=torch.float32)
+        if self.row_norm:
+            self.q_norm_w, self.k_norm_w = params[n["q_norm"]].to(**f32).contiguous(), params[n["k_norm"]].to(**f32).contiguous()
+        if self.distance_bias is not None:
+            self.bias_table = distance_bias_table(params[n["rel"]], float(self.distance_bias["max_distance"]), self.window).to(**f32).contiguous()
+        if self.has_sink:
+            self.sink_w = params[n["sink"]].to(**f32).contiguous()
         if self.taps > 0:
             # tap-major [taps, channels]: the prepare kernel reads neighbouring channels' taps side by side
             self.filter_w = torch.cat([params[n["q_filter"]], params[n["k_filter"]], params[n["v_filter"]]], dim=0) \
@@ -156,12 +222,30 @@ class Attention(Mixer):
     def input_product(self):
         """The q/k/v(/gate) product, for a block that joins the products of parts reading the same rows. Only the
         prepared path reads its rows by (leading dimension, first column)."""
-        return (self.qkv, "compute") if self.prepared else None
+        return (self.qkv, "compute") if (self.prepared or self.biased) else None
 
     def drop_input_product(self):
         self.qkv = None
 
+    def _forward_biased(self, qkv, col0, step, cache, residual, write_cache):
+        """Row norms of q and k with the cache write in one kernel; then attention whose scores take the distance
+        bias and whose denominator takes the sink."""
+        table = step.block_tables[cache.group]
+        q = ops.rownorm_store(qkv, col0, self.q_norm_w, self.k_norm_w, float(self.row_norm_eps or 0.0), step, table,
+                              cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim, self.v_dim, write_cache)
+        ctx = None
+        if self.rt.fast("attention"):
+            ctx = ops.attention_window(q, cache.k, cache.v, table, step, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
+                                       self.window, self.scale, self.bias_table, self.sink_w)
+        if ctx is None:
+            ctx = ops.attention_plain(q, cache.k, cache.v, table, step.token_seg, step.positions, self.n_heads, self.n_kv,
+                                      self.head_dim, self.window, self.scale, step.status, self.v_dim, self.bias_table, self.sink_w)
+        return self._project_out(ctx, residual)
+
     def forward(self, x, step, cache, residual, write_cache=True):
+        if self.biased:
+            qkv, col0 = own_or_projected(self, x, self.qkv)
+            return self._forward_biased(qkv, col0, step, cache, residual, write_cache)
         if self.prepared:
             qkv, col0 = own_or_projected(self, x, self.qkv)
             return self._forward_prepared(qkv, col0, step, cache, residual, write_cache)

@@ -6,7 +6,12 @@ is float32; the sums happen in the parts' last matrix product, in float32.
 h += sigmoid(G1 n + g1) * mixer(n) + sigmoid(G2 n + g2) * feed_forward(n); the feed-forward (and its gate) may be
 absent. Slots: norm, mixer, gate (family "gate": the logits of both gates in one product), feed_forward. A mixer
 that is two mixers side by side hands over both results and their constants, so that the weighing, the gating and
-the residual sum are one float32 kernel."""
+the residual sum are one float32 kernel.
+
+"sublayer_norm": the sublayers read the residual stream h itself and the norm sits on what they RETURN:
+h += norm_a(mixer(h)); h += norm_b(feed_forward(h)); the feed-forward and its norm may be absent. Slots: mixer,
+mixer_out_norm, feed_forward, feed_forward_out_norm. Norm and sum are one float32 kernel, which also leaves h in the
+compute dtype for the next sublayer's first matrix product."""
 from __future__ import annotations
 
 import os
@@ -124,3 +129,42 @@ class ParallelGatedBlock(Block):
             p, q, a, b = self.mixer.forward(arg(self.mixer), step, cache, None, write_cache), None, 1.0, 1.0
         r = self.feed_forward.forward(arg(self.feed_forward), None) if self.feed_forward is not None else None
         return ops.gated_sum(h, gates, p, a, q, b, r, g0)
+
+
+@register_block("sublayer_norm")
+class SublayerNormBlock(Block):
+    def __init__(self, mixer, mixer_out_norm, feed_forward=None, feed_forward_out_norm=None):
+        parts = {"mixer": mixer, "mixer_out_norm": mixer_out_norm}
+        if feed_forward is not None:
+            if feed_forward_out_norm is None:
+                raise ValueError("a feed-forward in a sublayer_norm block needs its norm")
+            parts.update(feed_forward=feed_forward, feed_forward_out_norm=feed_forward_out_norm)
+        super().__init__(**parts)
+        self.feed_forward, self.feed_forward_out_norm = feed_forward, feed_forward_out_norm
+        for n in (mixer_out_norm, feed_forward_out_norm):
+            if n is not None and not getattr(n, "fusable", False):
+                raise ValueError("a sublayer_norm block needs norms of the (weight, eps) root-mean-square kind")
+
+    def forward(self, h, step, cache, write_cache=True):
+        from .. import ops
+        rt = self.mixer.rt
+        x = h if rt.dtype == torch.float32 else self._copy_of(h, step, rt.dtype)
+        fused = getattr(self.mixer, "forward_normed", None)
+        got = fused(x, step, cache, write_cache, h, self.mixer_out_norm, rt.dtype) if fused is not None else None
+        if got is None:
+            y = self.mixer.forward(x, step, cache, None, write_cache)
+            got = ops.norm_add(h, y, self.mixer_out_norm.weight, self.mixer_out_norm.eps, rt.dtype)
+        h, copy = got
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(copy if copy is not None else h, None)
+            h, copy = ops.norm_add(h, y, self.feed_forward_out_norm.weight, self.feed_forward_out_norm.eps, rt.dtype)
+        step.extras["rows_copy"] = (h, copy)
+        return h
+
+    @staticmethod
+    def _copy_of(h, step, dtype):
+        from .. import ops
+        have = step.extras.get("rows_copy")
+        if have is not None and have[0] is h and have[1] is not None and have[1].dtype == dtype:
+            return have[1]
+        return ops.cast_rows(h, dtype)

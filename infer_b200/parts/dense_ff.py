@@ -1,7 +1,8 @@
-"""Dense feed-forward with one hidden layer: out = residual + act(x Wup^T) Wdown^T, no biases.
+"""Dense feed-forward with one hidden layer: out = residual + act(x Wup^T) Wdown^T, no biases; with ``gated`` the
+hidden layer is act(x Wgate^T) * (x Wup^T) (gate and up are one matrix product).
 
-``activation``: "gelu_tanh" is 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  ``names`` renames the two matrices
-(roles up, down).
+``activation``: "gelu_tanh" is 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  ``names`` renames the matrices
+(roles up, down, gate).
 """
 from __future__ import annotations
 
@@ -13,7 +14,7 @@ from .base import FeedForward, own_or_projected, register_feed_forward
 from .linear import Linear
 
 _ACTIVATIONS = {"gelu_tanh": ops.gelu_tanh}        # each: (rows, first column, width) -> contiguous [T, width]
-_NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
+_NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "gate": "gate_proj.weight"}
 
 
 @register_feed_forward("dense")
@@ -28,18 +29,23 @@ class DenseFeedForward(FeedForward):
         act = spec.get("activation", "gelu_tanh")
         if act not in _ACTIVATIONS:
             raise ValueError(f"activation {act!r} is not among {sorted(_ACTIVATIONS)}")
-        self.activation = _ACTIVATIONS[act]
+        self.activation, self.act_name = _ACTIVATIONS[act], act
+        self.gated = bool(spec.get("gated", False))
         self.up = self.down = None
 
     @classmethod
     def param_shapes(cls, spec):
         H, I = int(spec["hidden_size"]), int(spec["intermediate_size"])
         n = {**_NAMES, **dict(spec.get("names") or {})}
-        return {n["up"]: (I, H), n["down"]: (H, I)}
+        shapes = {n["up"]: (I, H), n["down"]: (H, I)}
+        if spec.get("gated", False):
+            shapes[n["gate"]] = (I, H)
+        return shapes
 
     def load(self, params):
         n = {**_NAMES, **dict(self.spec.get("names") or {})}
-        self.up = Linear(self.rt, params[n["up"]])
+        # gated: result rows [gate | up]
+        self.up = Linear(self.rt, torch.cat([params[n["gate"]], params[n["up"]]], dim=0) if self.gated else params[n["up"]])
         self.down = Linear(self.rt, params[n["down"]])
 
     def input_product(self):
@@ -50,7 +56,10 @@ class DenseFeedForward(FeedForward):
 
     def forward(self, x, residual):
         rows, c0 = own_or_projected(self, x, self.up)
-        act = self.activation(rows, c0, self.inter)
+        if self.gated:
+            act = ops.glu_act(rows, c0, c0 + self.inter, self.inter, self.act_name)
+        else:
+            act = self.activation(rows, c0, self.inter)
         if residual is None:
             return self.down(act, out_dtype=torch.float32)
         return self.down(act, residual=residual)

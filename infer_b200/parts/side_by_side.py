@@ -3,6 +3,10 @@
 The spec holds the two mixers' own specs under ``first`` and ``second`` (family "mixer", any registered kinds; their
 prefixes are relative to this part's) and the two constants.  Each keeps its own pages or state: the part's need is
 the two needs by name.  Tensors are declared and loaded through the two mixers' classes.
+
+With ``first_norm`` / ``second_norm`` (local names of two weights [hidden_size]) and ``norm_eps``, each result is
+divided by its root mean square over the width and multiplied by its weight before the two are weighed and added:
+a * first(x) / rms * w1 + b * second(x) / rms * w2.
 """
 from __future__ import annotations
 
@@ -21,6 +25,12 @@ class SideBySide(Mixer):
         self.sides = {s: build_part("mixer", spec[s], runtime) for s in _SIDES}
         self.scales = {"first": float(spec.get("first_scale", 1.0)), "second": float(spec.get("second_scale", 1.0))}
         self.graph_safe = all(getattr(m, "graph_safe", True) for m in self.sides.values())
+        self.norm_names = {s: spec.get(s + "_norm") for s in _SIDES}
+        self.normed = any(v is not None for v in self.norm_names.values())
+        if self.normed and (None in self.norm_names.values() or not float(spec.get("norm_eps") or 0.0) > 0):
+            raise ValueError("side_by_side norms need both weights' names, hidden_size and a positive norm_eps")
+        self.norm_eps = float(spec.get("norm_eps") or 0.0)
+        self.norm_w = {}
 
     @classmethod
     def param_shapes(cls, spec):
@@ -29,10 +39,15 @@ class SideBySide(Mixer):
             sub = spec[s]
             for local, shape in part_class("mixer", sub.kind).param_shapes(sub).items():
                 shapes[sub.prefix + local] = shape
+        for s in _SIDES:
+            if spec.get(s + "_norm") is not None:
+                shapes[str(spec[s + "_norm"])] = (int(spec["hidden_size"]),)
         return shapes
 
     @classmethod
     def init_params(cls, spec, name, shape, gen):
+        if name in (spec.get("first_norm"), spec.get("second_norm")):
+            return 1.0 + 0.1 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
         for s in _SIDES:
             sub = spec[s]
             sub_cls = part_class("mixer", sub.kind)
@@ -44,6 +59,8 @@ class SideBySide(Mixer):
         for s, m in self.sides.items():
             sub = self.spec[s]
             m.load({local: params[sub.prefix + local] for local in type(m).param_shapes(sub)})
+            if self.normed:
+                self.norm_w[s] = params[str(self.norm_names[s])].to(device=self.rt.device, dtype=torch.float32).contiguous()
 
     def members(self):
         """The two mixers, for a block that joins first products across its parts."""
@@ -70,9 +87,22 @@ class SideBySide(Mixer):
             b = self.sides["second"].forward(arg(self.sides["second"]), step, cache["second"], None, write_cache)
         return a, b, self.scales["first"], self.scales["second"]
 
+    def forward_normed(self, x, step, cache, write_cache, h, out_norm, copy_dtype):
+        """For a block that normalises what the mixer returns and adds it to h: with norms on the two sides, the two
+        norms, the weighing, the block's norm and the sum are one kernel. Returns (h, its copy in copy_dtype) or None."""
+        if not self.normed:
+            return None
+        from .. import ops
+        a, b, sa, sb = self.forward_sides(x, step, cache, write_cache)
+        return ops.dual_norm_sum(a, self.norm_w["first"], sa, b, self.norm_w["second"], sb, self.norm_eps, h, out_norm.weight,
+                                 out_norm.eps, copy_dtype)
+
     def forward(self, x, step, cache, residual, write_cache=True):
         from .. import ops
         a, b, sa, sb = self.forward_sides(x, step, cache, write_cache)
+        if self.normed:
+            m, _ = ops.dual_norm_sum(a, self.norm_w["first"], sa, b, self.norm_w["second"], sb, self.norm_eps)
+            return m if residual is None else ops.gated_sum(residual, None, m)
         if residual is None:
             residual = torch.zeros_like(a)
         return ops.gated_sum(residual, None, a, sa, b, sb)

@@ -36,6 +36,13 @@ class WeightsError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def shape_fits(want, got) -> bool:
+    """True if a stored tensor's shape is the expected one; an expected size of -1 takes any size (the part reads it
+    from the tensor: a table whose number of rows, or a low-rank product whose rank, only the checkpoint states)."""
+    want, got = tuple(want), tuple(got)
+    return len(want) == len(got) and all(w == g or w == -1 for w, g in zip(want, got))
+
+
 def _part_entries(family: str, spec: PartSpec):
     """(full tensor name, shape, part class, part spec, local name) of one part, nested parts included."""
     cls = part_class(family, spec.kind)
@@ -66,7 +73,7 @@ def load_weights(model_dir: str, spec: ModelSpec) -> Dict[str, torch.Tensor]:
         missing = [n for n in sorted(want) if n not in have]
         unexpected = [n for n in sorted(have) if n not in want and n not in spec.optional_tensors]
         wrong = [(n, want[n][0], have[n].shape(n)) for n in sorted(want)
-                 if n in have and tuple(have[n].shape(n)) != tuple(want[n][0])]
+                 if n in have and not shape_fits(want[n][0], have[n].shape(n))]
         if missing or unexpected or wrong:
             raise WeightsError(model_dir, missing, unexpected, wrong)
         return {n: have[n].get(n) for n in want}
@@ -80,7 +87,7 @@ def check_weights(weights: Mapping[str, torch.Tensor], spec: ModelSpec, where: s
     missing = [n for n in sorted(want) if n not in weights]
     unexpected = [n for n in sorted(weights) if n not in want and n not in spec.optional_tensors]
     wrong = [(n, want[n][0], tuple(weights[n].shape)) for n in sorted(want)
-             if n in weights and tuple(weights[n].shape) != tuple(want[n][0])]
+             if n in weights and not shape_fits(want[n][0], weights[n].shape)]
     if missing or unexpected or wrong:
         raise WeightsError(where, missing, unexpected, wrong)
 
@@ -96,6 +103,9 @@ def random_weights(spec: ModelSpec, seed: int, dtype: torch.dtype = torch.bfloat
     for name, (shape, cls, ps, local) in expected_tensors(spec).items():
         gen = torch.Generator(device=device)
         gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
+        if any(n < 0 for n in shape):
+            raise ValueError(f"tensor {name} has a size that only a checkpoint states ({list(shape)}); "
+                             "a random model needs it in its configuration")
         out[name] = cls.init_params(ps, local, shape, gen).to(dtype)
     return out
 
