@@ -14,6 +14,11 @@ input-dependent factor per key channel) and ``window_and_delta`` (layer type "pa
 attention with a learned bias per distance bucket and a sink, beside a gated delta-rule recurrence behind short
 causal filters; each side normalised over the width, the mean of the two).
 Feed-forwards: ``dense_gated`` and ``routed_experts`` (softmax router, groups of neighbouring experts, a shared expert).
+
+``ROUNDING``: None computes exactly. Set to ``torch.bfloat16`` (see ``rounded``), activations are rounded where a
+bfloat16 serving path stores them (the rows a sublayer reads, q/k/v of attention and its contexts, hidden layers of
+feed-forwards, what a recurrence hands to its output matrix), which gives the size of the rounding noise such a path
+must have.
 """
 from __future__ import annotations
 
@@ -26,6 +31,28 @@ F = torch.float64
 UNIT_EPS = 1e-6            # inside the root when q and k of the delta rule are made unit vectors
 WEIGHT_SUM_EPS = 1e-20     # added to the sum of the chosen experts' scores
 EXPERT_SLOPE = 1.702       # g * sigmoid(EXPERT_SLOPE * g)
+
+
+ROUNDING = None
+
+
+class rounded:
+    """with rounded(torch.bfloat16): ... computes with activations rounded where a serving path stores them."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global ROUNDING
+        self.old, ROUNDING = ROUNDING, self.dtype
+
+    def __exit__(self, *exc):
+        global ROUNDING
+        ROUNDING = self.old
+
+
+def _rnd(x: torch.Tensor) -> torch.Tensor:
+    return x if ROUNDING is None else x.to(ROUNDING).to(x.dtype)
 
 
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -107,7 +134,7 @@ def decayed_linear_attention(h, m: Mapping, W: Mapping[str, torch.Tensor], p: st
     decay = torch.exp(torch.nn.functional.logsigmoid(z) / tau)         # sigmoid(z) ** (1 / tau)
     o = torch.stack([decayed_state_scan(q[:, i], k[:, i], v[:, i], decay[:, i])[0] for i in range(H)], dim=1)
     o = rms_weighted(o, W[p + "norm"], eps).reshape(T, H * dv)
-    return linear(o * silu(linear(h, W[p + "g"])), W[p + "o"])
+    return linear(_rnd(o * silu(linear(h, W[p + "g"]))), W[p + "o"])
 
 
 def distance_bucket(n: int, B: int, D: float) -> int:
@@ -123,16 +150,16 @@ def windowed_attention(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps
     scale from the configuration, a bias per (distance bucket, head), a window, a sink in the softmax denominator."""
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    q = rms_weighted(linear(h, W[p + "q"], W[p + "q.b"]), W[p + "q.norm"], eps).view(T, H, d)
-    k = rms_weighted(linear(h, W[p + "k"], W[p + "k.b"]), W[p + "k.norm"], eps).view(T, G, d)
-    v = linear(h, W[p + "v"], W[p + "v.b"]).view(T, G, dv)
+    q = _rnd(rms_weighted(_rnd(linear(h, W[p + "q"], W[p + "q.b"])), W[p + "q.norm"], eps)).view(T, H, d)
+    k = _rnd(rms_weighted(_rnd(linear(h, W[p + "k"], W[p + "k.b"])), W[p + "k.norm"], eps)).view(T, G, d)
+    v = _rnd(linear(h, W[p + "v"], W[p + "v.b"])).view(T, G, dv)
     rel = W[p + "rel"].to(F)
     B = rel.shape[0]
     window = (m.get("mask") or {}).get("size")
     i = torch.arange(T)
     dist = i[:, None] - i[None, :]
     seen = (dist >= 0) & ((dist < window) if window else torch.ones_like(dist, dtype=torch.bool))
-    bucket = torch.tensor([[distance_bucket(int(n), B, float(m["bias_max"])) if n >= 0 else 0 for n in row] for row in dist.tolist()])
+    bucket = torch.tensor([distance_bucket(n, B, float(m["bias_max"])) for n in range(max(T, 1))])[dist.clamp(min=0)]
     out = torch.zeros(T, H, dv, dtype=F)
     for a in range(H):
         g = a // (H // G)
@@ -142,7 +169,7 @@ def windowed_attention(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps
         top = torch.maximum(s.max(dim=-1).values, sink)
         e = torch.exp(s - top[:, None])
         out[:, a] = (e / (e.sum(dim=-1) + torch.exp(sink - top))[:, None]) @ v[:, g]
-    return linear(out.reshape(T, H * dv), W[p + "o"])
+    return linear(_rnd(out.reshape(T, H * dv)), W[p + "o"])
 
 
 def gated_delta_rule(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps: float):
@@ -158,7 +185,7 @@ def gated_delta_rule(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps: 
     o = torch.stack([delta_rule_scan(q[:, i // (H // G)], k[:, i // (H // G)], v[:, i], g[:, i], beta[:, i])[0]
                      for i in range(H)], dim=1)
     o = rms_weighted(o, W[p + "norm"], eps).reshape(T, H * dv)
-    return linear(o * silu(linear(h, W[p + "g"])), W[p + "o"])
+    return linear(_rnd(o * silu(linear(h, W[p + "g"]))), W[p + "o"])
 
 
 def window_and_delta(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps: float):
@@ -170,13 +197,13 @@ def window_and_delta(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps: 
 # ----------------------------------------------------------------------------- feed-forwards
 
 def dense_gated(h, W: Mapping[str, torch.Tensor], p: str):
-    return linear(gelu_tanh(linear(h, W[p + "gate"])) * linear(h, W[p + "up"]), W[p + "down"])
+    return linear(_rnd(gelu_tanh(_rnd(linear(h, W[p + "gate"]))) * _rnd(linear(h, W[p + "up"]))), W[p + "down"])
 
 
 def clipped_expert(h, W: Mapping[str, torch.Tensor], p: str, limit: float):
-    g = torch.clamp(linear(h, W[p + "gate"]), max=limit)
-    u = torch.clamp(linear(h, W[p + "up"]), -limit, limit)
-    return linear(g * torch.sigmoid(EXPERT_SLOPE * g) * (u + 1.0), W[p + "down"])
+    g = torch.clamp(_rnd(linear(h, W[p + "gate"])), max=limit)
+    u = torch.clamp(_rnd(linear(h, W[p + "up"])), -limit, limit)
+    return linear(_rnd(g * torch.sigmoid(EXPERT_SLOPE * g) * (u + 1.0)), W[p + "down"])
 
 
 def route(h, mlp: Mapping, W: Mapping[str, torch.Tensor], p: str):
@@ -215,11 +242,21 @@ def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], tokens: Sequence[int], 
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         mixer = {"gla": decayed_linear_attention, "parallel": window_and_delta}[layer["type"]]
-        x = x + rms_weighted(mixer(x, layer["mixer"], W, p + "mix.", eps), W[p + "norm1"], eps)
+        x = x + rms_weighted(mixer(_rnd(x), layer["mixer"], W, p + "mix.", eps), W[p + "norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = dense_gated(x, W, p + "mlp.") if mlp["kind"] == "dense" else routed_experts(x, mlp, W, p + "mlp.")
+            y = dense_gated(_rnd(x), W, p + "mlp.") if mlp["kind"] == "dense" else routed_experts(_rnd(x), mlp, W, p + "mlp.")
             x = x + rms_weighted(y, W[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    return linear(rms_weighted(x, W["final.norm"], eps), W["head"])
+    return linear(_rnd(rms_weighted(x, W["final.norm"], eps)), W["head"])
+
+
+def greedy(cfg: Mapping, W: Mapping[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:
+    """n_new tokens, each the first index of the largest logit after the whole sequence so far."""
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(cfg, W, ids)[-1]))
+        ids.append(tok)
+        out.append(tok)
+    return out
