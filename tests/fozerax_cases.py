@@ -100,13 +100,35 @@ def oracle(cfg: dict, seed: int, compute: torch.dtype, ids: Sequence[int], round
                    "none" if rounding is None else n(rounding))
 
 
+CLOSE_CALL = 0.02      # a router's gap, in units of its logits' terms, below which bfloat16 roundings may turn the choice
+
+
+@functools.lru_cache(maxsize=64)
+def _router_gaps(cfg_json: str, seed: int, sharp: float, ids: Tuple[int, ...]) -> np.ndarray:
+    cfg = json.loads(cfg_json)
+    W = H.as_compute(make_weights(cfg, seed, torch.bfloat16, sharp), torch.bfloat16)
+    gaps: List[torch.Tensor] = []
+    pf.forward(cfg, W, list(ids), None, gaps)
+    return torch.stack(gaps).min(dim=0).values.numpy() if gaps else np.full(len(ids), np.inf)
+
+
 def check(cfg: dict, seed: int, dtype: torch.dtype, got: Dict[str, Dict[int, np.ndarray]], reqs: Dict[str, List[int]],
           sharp: float = 0.0, what: str = ""):
+    """The engine's rows against the plain implementation. In bfloat16, positions at which a router's choice is a
+    close call are left out (the other expert is as right an answer there). The float32 comparison leaves out nothing
+    and is the sharp one; cuttings are compared bit by bit there."""
     for rid, ids in reqs.items():
         ref = oracle(cfg, seed, dtype, ids, None, sharp)
         rows = sorted(got[rid])
+        if dtype != torch.float32:
+            gaps = _router_gaps(json.dumps(cfg, sort_keys=True), seed, float(sharp), tuple(int(i) for i in ids))
+            clear = [p for p in rows if gaps[p] >= CLOSE_CALL]
+            assert len(clear) >= 0.6 * len(rows) - 1, f"{what}/{rid}: {len(rows) - len(clear)} of {len(rows)} positions are close calls"
+            rows = clear
+            if not rows:
+                continue
         g = np.stack([got[rid][p] for p in rows])
         if dtype == torch.float32:
             H.check_f32(g, ref[rows], f"{what}/{rid}")
         else:
-            check_bf16(g, ref[rows], oracle(cfg, seed, dtype, ids, torch.bfloat16, sharp)[rows], f"{what}/{rid}")
+            check_bf16(g, ref[rows], oracle(cfg, seed, dtype, ids, torch.bfloat16, sharp)[rows], f"{what}/{rid}", factor=4.0)

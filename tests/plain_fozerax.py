@@ -176,9 +176,10 @@ def gated_delta_rule(h, m: Mapping, W: Mapping[str, torch.Tensor], p: str, eps: 
     """Right side of layer type "parallel"."""
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    q = silu(causal_filter(linear(h, W[p + "q"]), W[p + "q.conv"])).view(T, G, d)
-    k = silu(causal_filter(linear(h, W[p + "k"]), W[p + "k.conv"])).view(T, G, d)
-    v = silu(causal_filter(linear(h, W[p + "v"]), W[p + "v.conv"])).view(T, H, dv)
+    filt = (lambda u, name: causal_filter(u, W[p + name])) if m.get("conv") else (lambda u, name: u)      # conv 0: no filter
+    q = silu(filt(linear(h, W[p + "q"]), "q.conv")).view(T, G, d)
+    k = silu(filt(linear(h, W[p + "k"]), "k.conv")).view(T, G, d)
+    v = silu(filt(linear(h, W[p + "v"]), "v.conv")).view(T, H, dv)
     q, k = unit(q) * d ** -0.5, unit(k)
     beta = torch.sigmoid(linear(h, W[p + "b"]))                                              # [T, H]
     g = torch.exp(-torch.exp(W[p + "A_log"].to(F)) * torch.nn.functional.softplus(linear(h, W[p + "a"]) + W[p + "dt_bias"].to(F)))
@@ -220,6 +221,35 @@ def route(h, mlp: Mapping, W: Mapping[str, torch.Tensor], p: str):
     return chosen, w / (w.sum(dim=-1, keepdim=True) + WEIGHT_SUM_EPS)
 
 
+def route_margin(h, mlp: Mapping, W: Mapping[str, torch.Tensor], p: str) -> torch.Tensor:
+    """Per token, how close the router's choice is to another one: the smallest gap between the logit of the last
+    group kept (its best expert) and the best group not kept, and between the last expert chosen and the best allowed
+    one not chosen, each divided by the size of the two logits' terms, |Wa * x| + |Wb * x| (what a relative rounding
+    of x moves them by). Infinite where there is no alternative. A comparison of roundings leaves out tokens whose gap
+    is within the rounding."""
+    r = mlp["router"]
+    E, top = r["experts"], r["top"]
+    Wr = W[p + "router"].to(F)
+    z = linear(h, Wr)
+    size = torch.sqrt(((h[:, None, :] * Wr[None, :, :]) ** 2).sum(dim=-1))                  # [T, E]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    per, T = E // groups["count"], h.shape[0]
+    gap = torch.full((T,), math.inf, dtype=F)
+
+    def rel(a, b):
+        return (z.gather(1, a[:, None]) - z.gather(1, b[:, None]))[:, 0] / (size.gather(1, a[:, None]) + size.gather(1, b[:, None]))[:, 0]
+    gz, garg = z.view(T, groups["count"], per).max(dim=-1)
+    order = gz.argsort(dim=-1, descending=True)
+    expert_of = lambda g: g * per + garg.gather(1, g[:, None])[:, 0]
+    if groups["keep"] < groups["count"]:
+        gap = rel(expert_of(order[:, groups["keep"] - 1]), expert_of(order[:, groups["keep"]]))
+    allowed = torch.zeros(T, groups["count"], dtype=torch.bool).scatter_(1, order[:, :groups["keep"]], True).repeat_interleave(per, dim=1)
+    ranked = z.masked_fill(~allowed, -math.inf).argsort(dim=-1, descending=True)
+    if top < groups["keep"] * per:
+        gap = torch.minimum(gap, rel(ranked[:, top - 1], ranked[:, top]))
+    return gap
+
+
 def routed_experts(h, mlp: Mapping, W: Mapping[str, torch.Tensor], p: str):
     chosen, w = route(h, mlp, W, p)
     out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=F)
@@ -235,8 +265,10 @@ def routed_experts(h, mlp: Mapping, W: Mapping[str, torch.Tensor], p: str):
 
 # ----------------------------------------------------------------------------- the model
 
-def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[List] = None) -> torch.Tensor:
-    """Logits [T, vocab] (float64) of one whole sequence. ``layers_out`` collects the residual stream after every layer."""
+def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[List] = None,
+            margins_out: Optional[List] = None) -> torch.Tensor:
+    """Logits [T, vocab] (float64) of one whole sequence. ``layers_out`` collects the residual stream after every layer,
+    ``margins_out`` the routers' gaps per token (``route_margin``), one tensor per routed layer."""
     eps = float(cfg["norm"]["eps"])
     x = rms_weighted(W["embed"].to(F)[torch.as_tensor(list(tokens), dtype=torch.long)], W["embed.norm"], eps)
     for i, layer in enumerate(cfg["layers"]):
@@ -246,6 +278,8 @@ def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], tokens: Sequence[int], 
         mlp = layer.get("mlp")
         if mlp is not None:
             y = dense_gated(_rnd(x), W, p + "mlp.") if mlp["kind"] == "dense" else routed_experts(_rnd(x), mlp, W, p + "mlp.")
+            if margins_out is not None and mlp["kind"] != "dense":
+                margins_out.append(route_margin(_rnd(x), mlp, W, p + "mlp."))
             x = x + rms_weighted(y, W[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
