@@ -3,6 +3,7 @@ random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L] [--impl reference]
     python bench.py --design ruvenex [--sizes 1.5b|7b] [--layers L]     (another design beside Qwen2 at equal sizes)
+    python bench.py --design fozerax [--sizes 1.5b|7b] [--layers L]     (beside Ruvenex, the closest design, and Qwen2)
 
 Prints ONE JSON line. "value" is decoded tokens per second of the step function, timed on the device with CUDA
 events around K decode steps of a batch of 8 requests whose 2,048-token contexts already lie in the paged cache
@@ -33,7 +34,9 @@ def _preset(name):
 
 SIZES = {"1.5b": _preset("qwen2.5-1.5b"), "7b": _preset("qwen2.5-7b"), "14b": _preset("qwen2.5-14b")}
 # Other designs at the same layer sizes (width, heads, feed-forward), for --design.
-DESIGNS = {"ruvenex": {"1.5b": "ruvenex-1.5b", "7b": "ruvenex-7b"}}
+DESIGNS = {"ruvenex": {"1.5b": "ruvenex-1.5b", "7b": "ruvenex-7b"}, "fozerax": {"1.5b": "fozerax-1.5b", "7b": "fozerax-7b"}}
+# the designs a design is measured beside, besides Qwen2: the closest one the engine has
+BESIDE = {"fozerax": ["ruvenex"]}
 CONFIG = SIZES["1.5b"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -362,9 +365,38 @@ def reference_arm(args):
     return 0
 
 
+def fozerax_flops(cfg, T):
+    """Arithmetic of a prompt of T tokens through a Fozerax configuration: matrix products (every expert's matrices
+    run for every token), windowed attention scores and sums, the recurrences' state updates and read-outs."""
+    W, total = cfg["width"], 0.0
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        if l["type"] == "gla":
+            hd, hv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            total += 2 * T * W * (2 * hd + 3 * hv + m.get("rank", 16)) + 2 * T * hd * m.get("rank", 16)
+            total += T * hd * m["vdim"] * 5
+        else:
+            a, r = m["left"], m["right"]
+            n = (a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"] + a["heads"] * a["vdim"]
+            n += 2 * r["kv_heads"] * r["dim"] + 3 * r["heads"] * r["vdim"] + 2 * r["heads"]
+            total += 2 * T * W * n
+            win = min(T, (a.get("mask") or {}).get("size") or T)
+            total += 2 * a["heads"] * (a["dim"] + a["vdim"]) * (T * win - win * (win - 1) / 2)
+            total += T * r["heads"] * r["dim"] * r["vdim"] * 8
+        f = l["mlp"]
+        if f and f["kind"] == "dense":
+            total += 2 * T * W * 3 * f["ff"]
+        elif f:
+            cols = f["router"]["experts"] * f["expert"]["ff"] + (f["shared"]["ff"] if f.get("shared") else 0)
+            total += 2 * T * W * (3 * cols + f["router"]["experts"])
+    return total + 2 * W * cfg["vocab"]
+
+
 def design_flops(cfg, T):
     """Arithmetic of a prompt of T tokens through a model of --design's configuration (matrix products, attention
     scores and sums, the recurrence's state updates and read-outs), logits at the last place only."""
+    if cfg.get("architecture") == "Fozerax":
+        return fozerax_flops(cfg, T)
     W, total = cfg["width"], 0.0
     for l in cfg["layers"]:
         a, r = l["mixer"]["left"], l["mixer"]["right"]
@@ -396,7 +428,9 @@ def design_arm(args, pk):
         else:
             print(json.dumps({"design": args.design, "mode": "prefill", "tokens": T, "ms": round(time_prefill(eng, T, max(1, args.steps), args.warmup), 3)}))
         return 0
-    for label, preset in ((args.design, _preset(DESIGNS[args.design][args.sizes])), ("qwen2", SIZES[args.sizes])):
+    arms = [(args.design, _preset(DESIGNS[args.design][args.sizes]))]
+    arms += [(d, _preset(DESIGNS[d][args.sizes])) for d in BESIDE.get(args.design, [])] + [("qwen2", SIZES[args.sizes])]
+    for label, preset in arms:
         CONFIG = preset
         n_all = len(preset["layers"]) if isinstance(preset.get("layers"), list) else preset["num_hidden_layers"]
         n_layers = args.layers or n_all

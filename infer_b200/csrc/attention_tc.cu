@@ -195,6 +195,11 @@ struct Params {
     int split;
     float* workspace;                        // [segments of two or more tokens][heads][query tiles][split][PART_FLOATS]
     unsigned int* counters;                  // [segments of two or more tokens][heads][query tiles], zero between launches
+    // Optional. A bias per (head, distance) added to the scaled score of query i and key j: bias[h * bias_len +
+    // min(i - j, bias_len - 1)], stored divided by the scale, so that it is added to the raw score. A sink per head:
+    // a logit without key or value that enters the softmax denominator once (the part that holds the first keys counts it).
+    const float* bias; int bias_len;
+    const float* sink;
 };
 constexpr int MAX_SPLIT = 4;
 constexpr int PART_MIN_TILES = 4;
@@ -396,6 +401,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int row_pos = q_first + r;
         const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
         float m_ref = -INFINITY, l = 0.0f;               // reference maximum of this row's O and P; sum of probabilities
+        if (p.sink && part == 0) {                       // the sum starts with the sink's exp(0) under its own logit
+            m_ref = p.sink[h] * LOG2E;
+            l = 1.0f;
+        }
+        const float* bias_h = p.bias ? p.bias + int64_t(h) * p.bias_len : nullptr;
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
             const int key0 = (kt0 + j) * BN;
@@ -410,6 +420,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             for (int c = 0; c < BN; c += 16) tmem_ld16(lane_addr + S_COL + (j & 1) * BN + c, reinterpret_cast<uint32_t*>(s + c));
             tmem_ld_wait();
             IB_T(j, 2);
+            if (bias_h) {
+                // (lanes of a warp are neighbouring rows: one column's biases are neighbouring floats)
+                const int d0 = row_pos - key0, top = p.bias_len - 1;
+#pragma unroll
+                for (int c = 0; c < BN; c++) s[c] += __ldg(bias_h + min(max(d0 - c, 0), top));
+            }
             const bool full_tile = key0 + BN - 1 <= q_first && key0 >= (p.window > 0 ? max(0, q_first + BM - 1 - p.window + 1) : 0);
             // Raw scores: the scale goes into the exponent's multiply-add below. Most tiles lie wholly below the diagonal
             // and inside the window and need no mask. (Masks are written without short-circuit operators: a branch per
@@ -603,12 +619,14 @@ IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
 // split: up to how many CTAs share the key tiles of one query tile (1: none); it is lowered to what the workspace
 // (floats) and the counters (zero before and after) have room for: one slot per segment of two or more tokens
 // (n_long_segments of them; 0: assume all), head and query tile.
-IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
-                                      int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
-                                      int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
-                                      int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
-                                      int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments) {
+static int prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                      int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
+                      int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
+                      int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
+                      int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments,
+                      const float* bias, int bias_len, const float* sink) {
     if (n_segments <= 0 || max_q_len <= 1) return IB_OK;
+    if (bias && (bias_len <= 0 || !(scale > 0.0f))) return ib::fail(IB_ERR_ARG, "attention_tc: a distance bias needs rows and a positive scale");
     if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_tc: built for head_dim %d, called with %d", HD, head_dim);
     if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_tc: pages must hold %d positions, got %d", PAGE, page_size);
     if (n_kv <= 0 || n_heads % n_kv) return ib::fail(IB_ERR_ARG, "attention_tc: heads %d not a multiple of kv heads %d", n_heads, n_kv);
@@ -633,6 +651,7 @@ IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const 
     p.out = (bf16*)out; p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
     p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
     p.n_pages = n_pages; p.status = status;
+    p.bias = bias; p.bias_len = bias_len; p.sink = sink;
     // Sharing query tiles needs scratch for every (segment, head, query tile); with less than that, fewer parts.
     if (n_long_segments <= 0 || n_long_segments > n_segments) n_long_segments = n_segments;
     const int64_t n_qt = (max_q_len + BM - 1) / BM, tiles = int64_t(n_long_segments) * n_heads * n_qt;
@@ -644,6 +663,29 @@ IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const 
     p.early_release = int64_t(n_segments) * n_heads * n_qt * split <= 296 ? 1 : 0;
     const dim3 grid{unsigned(n_heads), unsigned(n_qt * split), unsigned(n_segments)};
     return ib::launch("attention_tc", attn_prefill_tc_kernel, grid, dim3(NUM_THREADS), size_t(SMEM_BYTES), stream, 1u, mq, mk, mv, p);
+}
+
+IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                                      int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
+                                      int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
+                                      int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
+                                      int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments) {
+    return prefill_tc(q, k_cache, v_cache, out, block_table, max_blocks, seg_start, seg_pos0, n_segments, n_tokens, n_heads, n_kv,
+                      head_dim, page_size, window, scale, n_pages, max_q_len, status, stream, split, workspace, workspace_floats,
+                      counters, n_counters, n_long_segments, nullptr, 0, nullptr);
+}
+
+// The same with a bias per (head, distance), float [heads, bias_len], ALREADY DIVIDED by the scale (it is added to the
+// raw score; a distance beyond the table takes its last entry), and / or a sink logit per head, float [heads].
+IB_EXPORT int ib_attention_prefill_tc_biased(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                                             int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
+                                             int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
+                                             int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
+                                             int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments,
+                                             const float* bias, int bias_len, const float* sink) {
+    return prefill_tc(q, k_cache, v_cache, out, block_table, max_blocks, seg_start, seg_pos0, n_segments, n_tokens, n_heads, n_kv,
+                      head_dim, page_size, window, scale, n_pages, max_q_len, status, stream, split, workspace, workspace_floats,
+                      counters, n_counters, n_long_segments, bias, bias_len, sink);
 }
 
 #ifdef IB_ATTN_TRACE

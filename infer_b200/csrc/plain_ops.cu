@@ -324,8 +324,14 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
                  const int* __restrict__ positions, T* __restrict__ out, int n_heads, int n_kv, int head_dim, int v_dim,
                  int page_size, int window, float scale, int64_t n_pages, int* status,
-                 const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ sink) {
+                 const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ sink,
+                 const int* __restrict__ single_only) {
     ib::pdl_wait();
+    // single_only (a step's seg_start): tokens of segments with two or more tokens are another kernel's
+    if (single_only) {
+        const int sg = token_seg[blockIdx.x];
+        if (single_only[sg + 1] - single_only[sg] > 1) return;
+    }
     extern __shared__ float smem[];
     float* qs = smem;                      // [head_dim], rounded up to an even count: the 8-byte rows behind stay aligned
     float* ps = qs + ((head_dim + 1) & ~1);   // [AT]
@@ -700,7 +706,7 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
                                  int64_t max_blocks, const int* token_seg, const int* positions, void* out,
                                  int64_t n_tokens, int n_heads, int n_kv, int head_dim, int page_size, int window,
                                  float scale, int64_t n_pages, int dtype, int* status, cudaStream_t stream, int v_dim,
-                                 const float* dist_bias, int bias_len, const float* sink) {
+                                 const float* dist_bias, int bias_len, const float* sink, const int* single_only) {
     if (n_tokens <= 0) return IB_OK;
     if (dist_bias && bias_len <= 0) return ib::fail(IB_ERR_ARG, "ib_attention_plain: a distance bias needs at least one row");
     if (v_dim <= 0) v_dim = head_dim;                       // values as long as keys
@@ -713,11 +719,11 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
     if (dtype == IB_F32)
         IB_LAUNCH(attention_kernel<float>, grid, AT, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status,
-            dist_bias, bias_len, sink);
+            dist_bias, bias_len, sink, single_only);
     else if (dtype == IB_BF16)
         IB_LAUNCH(attention_kernel<bf16>, grid, AT, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
             block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status,
-            dist_bias, bias_len, sink);
+            dist_bias, bias_len, sink, single_only);
     else
         return ib::fail(IB_ERR_ARG, "ib_attention_plain: unknown dtype %d", dtype);
     return ib::check_launch("ib_attention_plain");

@@ -189,11 +189,14 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     token_seg: torch.Tensor, positions: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                     window: Optional[int], scale: float, status: Optional[torch.Tensor] = None,
                     v_head_dim: Optional[int] = None, dist_bias: Optional[torch.Tensor] = None,
-                    sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sink: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    single_only: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every token over its request's pages; returns [T, heads*v_head_dim] (values are as long
     as keys unless ``v_head_dim`` says otherwise; the value pages are [pages, kv_heads, page_size, v_head_dim]).
     ``dist_bias`` float32 [L, heads]: row min(distance, L - 1) is added to the scaled scores of a query's keys;
-    ``sink`` float32 [heads]: a logit per head that enters the softmax denominator only."""
+    ``sink`` float32 [heads]: a logit per head that enters the softmax denominator only. ``out``: write there;
+    ``single_only`` (the step's seg_start): only tokens that are a segment of their own are computed, the other rows
+    of ``out`` stay as they are."""
     _check(q, "q")
     T = q.shape[0]
     vd = int(v_head_dim or head_dim)
@@ -206,7 +209,10 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     _check(positions, "positions", torch.int32, (T,))
     _check(token_seg, "token_seg", torch.int32, (T,))
     _check(block_table, "block_table", torch.int32)
-    out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
+    else:
+        _check(out, "out", q.dtype, (T, n_heads * vd))
     if dist_bias is not None:
         _check(dist_bias, "dist_bias", torch.float32)
         if dist_bias.dim() != 2 or dist_bias.shape[1] != n_heads:
@@ -214,11 +220,11 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if sink is not None:
         _check(sink, "sink", torch.float32, (n_heads,))
     f = _fn("plain", "ib_attention_plain", [c_void_p] * 4 + [c_int64] + [c_void_p] * 3 + [c_int64] + [c_int] * 5 +
-            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p])
+            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p])
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           token_seg.data_ptr(), positions.data_ptr(), out.data_ptr(), T, n_heads, n_kv, head_dim, page_size,
           int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream(), vd,
-          _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink))
+          _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink), _ptr(single_only))
     return out
 
 
@@ -582,10 +588,23 @@ def rownorm_store(rows: torch.Tensor, col0: int, wq: Optional[torch.Tensor], wk:
 
 
 def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
-                     dist_bias, sink):
-    """A faster kernel for attention with a distance bias and a sink where it takes the shape; None where it does not
-    (the caller then uses the plain kernel)."""
-    return None
+                     dist_bias, sink, dist_bias_by_head=None):
+    """Attention with a distance bias and a sink on the tensor-core kernel for prompt portions, where it takes the
+    shape (bfloat16, keys and values of one size that the kernel is built for, a step that has portions); one-token
+    segments of the same step go through the plain kernel into the same rows. None where the shape is refused (the
+    caller then uses the plain kernel for everything). ``dist_bias_by_head``: float32 [heads, L], the bias divided
+    by the scale."""
+    from . import fast_ops
+    if step.max_q_len <= 1 or v_head_dim != head_dim or (dist_bias is not None and dist_bias_by_head is None):
+        return None
+    out = fast_ops.attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, window, scale,
+                                            dist_bias_by_head, sink)
+    if out is None:
+        return None
+    if any(n == 1 for n in step.seg_lens):
+        attention_plain(q, k_cache, v_cache, block_table, step.token_seg, step.positions, n_heads, n_kv, head_dim, window, scale,
+                        step.status, v_head_dim, dist_bias, sink, out, step.seg_start)
+    return out
 
 
 def decay_gates(rows: torch.Tensor, q_col: int, low_col: int, rank: int, up: torch.Tensor, bias: Optional[torch.Tensor],

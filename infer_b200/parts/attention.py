@@ -127,7 +127,7 @@ class Attention(Mixer):
             self.biased = True
         else:
             self.biased = False
-        self.q_norm_w = self.k_norm_w = self.bias_table = self.sink_w = None
+        self.q_norm_w = self.k_norm_w = self.bias_table = self.bias_by_head = self.sink_w = None
         self.n_qkv = (self.n_heads + self.n_kv) * self.head_dim + self.n_kv * self.v_dim
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
@@ -190,6 +190,8 @@ class Attention(Mixer):
             self.q_norm_w, self.k_norm_w = params[n["q_norm"]].to(**f32).contiguous(), params[n["k_norm"]].to(**f32).contiguous()
         if self.distance_bias is not None:
             self.bias_table = distance_bias_table(params[n["rel"]], float(self.distance_bias["max_distance"]), self.window).to(**f32).contiguous()
+            # for the tensor-core kernel: a head's biases side by side, divided by the scale (added to the raw score)
+            self.bias_by_head = (self.bias_table / self.scale).t().contiguous() if self.scale > 0 else None
         if self.has_sink:
             self.sink_w = params[n["sink"]].to(**f32).contiguous()
         if self.taps > 0:
@@ -236,7 +238,7 @@ class Attention(Mixer):
         ctx = None
         if self.rt.fast("attention"):
             ctx = ops.attention_window(q, cache.k, cache.v, table, step, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
-                                       self.window, self.scale, self.bias_table, self.sink_w)
+                                       self.window, self.scale, self.bias_table, self.sink_w, self.bias_by_head)
         if ctx is None:
             ctx = ops.attention_plain(q, cache.k, cache.v, table, step.token_seg, step.positions, self.n_heads, self.n_kv,
                                       self.head_dim, self.window, self.scale, step.status, self.v_dim, self.bias_table, self.sink_w)

@@ -166,15 +166,70 @@ def test_attention_with_distance_bias_window_and_sink(dtype, window):
     out = ops.attention_plain(q[rows].reshape(len(rows), H * d).to(dtype).to(DEV).contiguous(), kc.to(DEV), vc.to(DEV), table, step_seg, pos,
                               H, G, d, window, scale, None, dv, bias, sink.to(DEV)).double().cpu().view(len(rows), H, dv)
     assert torch.allclose(out, want[rows], **_tol(dtype))
-    for name, fn in (("window", getattr(ops, "attention_window_kernel", None)),):
-        if fn is None:
-            continue
-        st = _Step([len(rows)], [100], [0])
-        st.max_q_len, st.max_ctx_len = len(rows), n
-        out2 = fn(q[rows].reshape(len(rows), H * d).to(dtype).to(DEV).contiguous(), kc.to(DEV), vc.to(DEV), table, st, H, G, d, dv,
-                  window, scale, bias, sink.to(DEV))
-        if out2 is not None:
-            assert torch.allclose(out2.double().cpu().view(len(rows), H, dv), want[rows], **_tol(dtype)), name
+
+
+def _biased_attention(q, k, v, rel, sink, B, D, window, scale):
+    """Plain windowed attention of one sequence with a bucketed distance bias and a sink. q [n, H, d], k, v [n, G, .]."""
+    n, H = q.shape[:2]
+    G = k.shape[1]
+    idx = torch.arange(n)
+    dist = idx[:, None] - idx[None, :]
+    seen = (dist >= 0) & ((dist < window) if window else (dist >= 0))
+    bucket = torch.tensor([pf.distance_bucket(i, B, D) for i in range(n)])[dist.clamp(min=0)]
+    out = torch.zeros(n, H, v.shape[2], dtype=torch.float64)
+    for h in range(H):
+        s = (q[:, h] @ k[:, h // (H // G)].T) * scale + rel.double()[bucket, h]
+        s = s.masked_fill(~seen, -math.inf)
+        top = torch.maximum(s.max(dim=-1).values, sink.double()[h])
+        e = torch.exp(s - top[:, None])
+        out[:, h] = (e / (e.sum(dim=-1) + torch.exp(sink.double()[h] - top))[:, None]) @ v[:, h // (H // G)]
+    return out
+
+
+@pytest.mark.parametrize("window", [None, 33, 130, 300])
+@pytest.mark.parametrize("sizes", [(4, 2, 64), (8, 1, 128)])
+def test_tensor_core_attention_with_distance_bias_and_sink(sizes, window):
+    """A prompt portion of several query tiles behind a context, beside a one-token segment of another request: the
+    portion on the tensor-core kernel, the single token on the plain one, into one result; keys at the window's edges
+    stand out for two heads of the portion's last rows."""
+    from infer_b200.parts.attention import distance_bias_table
+    H, G, d = sizes
+    B, D, scale, dtype = 32, 120.0, 0.11, torch.bfloat16
+    g = torch.Generator().manual_seed(d + (window or 0))
+    n, m = 500, 90                                              # the portion's request; the single token's request
+    seqs = []
+    for length in (n, m):
+        seqs.append([torch.randn(length, hh, d, generator=g).to(dtype).double() for hh in (H, G, G)])
+    rel, sink = torch.randn(B, H, generator=g), torch.randn(H, generator=g)
+    sink[1] = 5.0
+    q, k, v = seqs[0]
+    if window is not None:
+        for probe in (n - 1, n - 70):
+            k[probe - (window - 1), 0] = 4.0 * q[probe, 0] / q[probe, 0].norm() * math.sqrt(d) / (scale * math.sqrt(d)) * 0.3
+            k[probe - window, G - 1] = 4.0 * q[probe, H - 1] / q[probe, H - 1].norm() * math.sqrt(d) / (scale * math.sqrt(d)) * 0.3
+        seqs[0][1] = k = k.to(dtype).double()
+    want = [_biased_attention(*sq, rel, sink, B, D, window, scale) for sq in seqs]
+    tables = [list(range(3, 35)), [40, 36, 38, 37, 41, 39]]
+    kc, vc = _paged([s_[1] for s_ in seqs], [s_[2] for s_ in seqs], tables, 44, G, d, d, dtype)
+    width = 32
+    table = torch.full((2, width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    first = 230                                                 # the portion: positions 230 .. 499 (three query tiles, the last ragged)
+    step = _Step([n - first, 1], [first, m - 1], [0, 1])
+    step.seg_lens, step.seg_pos0 = step.lens, torch.tensor(step.pos0, dtype=torch.int32, device=DEV)
+    step.max_q_len, step.max_ctx_len = n - first, n
+    rows = torch.cat([q[first:].reshape(n - first, H * d), seqs[1][0][m - 1:].reshape(1, H * d)]).to(dtype).to(DEV).contiguous()
+    bias = distance_bias_table(rel, D, window).to(DEV)
+    by_head = (bias / scale).t().contiguous()
+    before = dict(ops.LAUNCH_KINDS)
+    out = ops.attention_window(rows, kc.to(DEV), vc.to(DEV), table.to(DEV), step, H, G, d, d, window, scale, bias, sink.to(DEV), by_head)
+    assert out is not None and ops.LAUNCH_KINDS["ib_attention_prefill_tc_biased"] == before.get("ib_attention_prefill_tc_biased", 0) + 1
+    assert int(step.status.item()) == 0
+    got = out.double().cpu().view(-1, H, d)
+    ref = torch.cat([want[0][first:], want[1][m - 1:]])
+    assert torch.allclose(got, ref, rtol=3e-2, atol=3e-2)
+    assert float((got - ref).pow(2).mean().sqrt()) < 4e-3
 
 
 @pytest.mark.parametrize("sizes", [(2, 16, 4), (1, 40, 3), (3, 128, 16)])
