@@ -136,6 +136,45 @@ __global__ void glu_act_kernel(const T* __restrict__ rows, int64_t ld, int64_t g
     out[i] = ib::from_f32<T>(y);
 }
 
+// The same for bfloat16 rows whose sizes and addresses allow 16-byte accesses: eight columns a thread (they lie in one
+// block, since `group` is a multiple of eight).
+__global__ void glu_act_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int64_t gate_col, int64_t up_col, int64_t width8,
+                                   int kind, float limit, float limit2, float slope, const float* __restrict__ scale,
+                                   int64_t group, int64_t n_groups, bf16* __restrict__ out, int64_t n8) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const int64_t t = i / width8, c = (i - t * width8) * 8;
+    const uint4 gu = *reinterpret_cast<const uint4*>(rows + t * ld + gate_col + c);
+    const uint4 uu = *reinterpret_cast<const uint4*>(rows + t * ld + up_col + c);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uu);
+    const int64_t e = group > 0 ? c / group : 0;
+    const float lim = (group > 0 && e >= n_groups) ? limit2 : limit;
+    const float sc = (kind == 1 && scale && e < n_groups) ? scale[t * n_groups + e] : 1.0f;
+    uint4 res;
+    __nv_bfloat162* rh = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float2 g2 = __bfloat1622float2(gh[k]), u2 = __bfloat1622float2(uh[k]);
+        float y[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            float g = j ? g2.y : g2.x, u = j ? u2.y : u2.x;
+            if (kind == 0) {
+                y[j] = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+            } else {
+                g = fminf(g, lim);
+                u = fminf(fmaxf(u, -lim), lim);
+                y[j] = g * sigmoid_(slope * g) * (u + 1.0f);
+                if (scale && e < n_groups) y[j] *= sc;
+            }
+        }
+        rh[k] = __floats2bfloat162_rn(y[0], y[1]);
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = res;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Router: scores = softmax(logits) over all experts; experts form n_groups groups of neighbours, a group's score is
 // its largest; only experts of the `keep` best groups can be chosen; the `top` largest of those are chosen (ties:
@@ -254,6 +293,190 @@ rownorm_store_kernel(const T* __restrict__ rows, int64_t ld, int col0, const flo
     for (int i = threadIdx.x; i < nv; i += blockDim.x) {
         const int h = i / dv, j = i - h * dv;
         v_cache[((int64_t(page) * n_kv + h) * page_size + place) * dv + j] = r[nq + nk + i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Paged attention of single tokens with a window, a bias per (distance, head) and a sink, keys split over CTAs: a
+// decoded token of a windowed layer reads a few hundred keys, which one CTA per (token, head) walks too slowly.
+// One CTA per (token, kv head, chunk of KC keys aligned to absolute multiples of KC); its `group` query heads share
+// every key and value row that is read. Score phase: a thread per key (16-byte loads of its row where the sizes
+// allow), the group's queries in shared memory; softmax per head by a warp; value phase: a thread per channel.
+// A chunk leaves (maximum, sum, unnormalised context) per head in the workspace; the merge kernel adds a token's
+// chunks in ascending order, counts the sink once and divides. What a token's result depends on is (window, position)
+// only. `single_only` (a step's seg_start): tokens of longer segments are skipped (another kernel's).
+constexpr int KC = 128;
+constexpr int GMAX = 16;
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&x)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&x)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(KC)
+split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                       const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
+                       const int* __restrict__ positions, const int* __restrict__ single_only, float* __restrict__ parts,
+                       int n_heads, int n_kv, int d, int dv, int page_size, int window, float scale, int64_t n_pages,
+                       const float* __restrict__ dist_bias, int bias_len, int n_chunks, int vec, int* status) {
+    ib::pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int g = blockIdx.y, ci = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sg = token_seg[t];
+    if (single_only && single_only[sg + 1] - single_only[sg] > 1) return;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int base = (lo / KC + ci) * KC;
+    if (base > pos) return;
+    const int group = n_heads / n_kv, h0 = g * group;
+    extern __shared__ __align__(16) float sm[];
+    float* qs = sm;                                     // [group][d]
+    float* sc = qs + group * ((d + 3) & ~3);            // [group][KC] scores, then probabilities
+    float* ml = sc + group * KC;                        // [group][2] maximum and sum
+    int64_t* rowoff = reinterpret_cast<int64_t*>(ml + 2 * GMAX);   // [KC]
+    const int dq = (d + 3) & ~3;
+    for (int i = tid; i < group * d; i += KC) {
+        const int gq = i / d, e = i - gq * d;
+        qs[gq * dq + e] = ib::to_f32(q[(t * n_heads + h0 + gq) * d + e]);
+    }
+    __syncthreads();
+    const int* table = block_table + int64_t(sg) * max_blocks;
+    const int key = base + tid;
+    const bool valid = key >= lo && key <= pos;
+    float acc[GMAX];
+#pragma unroll
+    for (int gq = 0; gq < GMAX; gq++) acc[gq] = 0.0f;
+    bool have = false;
+    if (valid) {
+        const int page = table[key / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (status) atomicExch(status, 3);
+            rowoff[tid] = 0;
+        } else {
+            have = true;
+            const int64_t row = (int64_t(page) * n_kv + g) * page_size + key % page_size;
+            rowoff[tid] = row;
+            const T* kr = k_cache + row * d;
+            if (vec) {
+                for (int e = 0; e < d; e += 8) {
+                    float kv[8];
+                    load8<T>(kr + e, kv);
+#pragma unroll
+                    for (int gq = 0; gq < GMAX; gq++) {
+                        if (gq < group) {
+                            const float4 a = *reinterpret_cast<const float4*>(qs + gq * dq + e);
+                            const float4 b = *reinterpret_cast<const float4*>(qs + gq * dq + e + 4);
+                            float x = acc[gq];
+                            x = fmaf(a.x, kv[0], x); x = fmaf(a.y, kv[1], x); x = fmaf(a.z, kv[2], x); x = fmaf(a.w, kv[3], x);
+                            x = fmaf(b.x, kv[4], x); x = fmaf(b.y, kv[5], x); x = fmaf(b.z, kv[6], x); x = fmaf(b.w, kv[7], x);
+                            acc[gq] = x;
+                        }
+                    }
+                }
+            } else {
+                for (int e = 0; e < d; e++) {
+                    const float kv = ib::to_f32(kr[e]);
+#pragma unroll
+                    for (int gq = 0; gq < GMAX; gq++)
+                        if (gq < group) acc[gq] = fmaf(qs[gq * dq + e], kv, acc[gq]);
+                }
+            }
+        }
+    } else {
+        rowoff[tid] = 0;
+    }
+#pragma unroll
+    for (int gq = 0; gq < GMAX; gq++) {
+        if (gq < group) {
+            float sv = -INFINITY;
+            if (have) {
+                sv = acc[gq] * scale;
+                if (dist_bias) sv += dist_bias[int64_t(min(pos - key, bias_len - 1)) * n_heads + h0 + gq];
+            }
+            sc[gq * KC + tid] = sv;
+        }
+    }
+    __syncthreads();
+    for (int gq = warp; gq < group; gq += KC / 32) {
+        float* row = sc + gq * KC;
+        float m = -INFINITY;
+        for (int j = lane; j < KC; j += 32) m = fmaxf(m, row[j]);
+        m = ib::warp_max(m);
+        float l = 0.0f;
+        for (int j = lane; j < KC; j += 32) {
+            const float pv = row[j] > -INFINITY ? expf(row[j] - m) : 0.0f;
+            row[j] = pv;
+            l += pv;
+        }
+        l = ib::warp_sum(l);
+        if (lane == 0) { ml[2 * gq] = m; ml[2 * gq + 1] = l; }
+    }
+    __syncthreads();
+    const int j0 = max(lo, base) - base, j1 = min(pos, base + KC - 1) - base;
+    for (int c = tid; c < dv; c += KC) {
+        float o[GMAX];
+#pragma unroll
+        for (int gq = 0; gq < GMAX; gq++) o[gq] = 0.0f;
+#pragma unroll 4
+        for (int j = j0; j <= j1; j++) {
+            const float vv = ib::to_f32(v_cache[rowoff[j] * dv + c]);
+#pragma unroll
+            for (int gq = 0; gq < GMAX; gq++)
+                if (gq < group) o[gq] = fmaf(sc[gq * KC + j], vv, o[gq]);
+        }
+#pragma unroll
+        for (int gq = 0; gq < GMAX; gq++)
+            if (gq < group) parts[((t * n_heads + h0 + gq) * n_chunks + ci) * int64_t(dv + 2) + 2 + c] = o[gq];
+    }
+    if (tid < group) {
+        float* dst = parts + ((t * n_heads + h0 + tid) * n_chunks + ci) * int64_t(dv + 2);
+        dst[0] = ml[2 * tid];
+        dst[1] = ml[2 * tid + 1];
+    }
+}
+
+// One warp per (token, head): the chunks' parts in ascending order, the sink, the division.
+template <typename T>
+__global__ void split_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ token_seg,
+                                             const int* __restrict__ positions, const int* __restrict__ single_only,
+                                             const float* __restrict__ sink, T* __restrict__ out, int64_t n_rows, int n_heads,
+                                             int dv, int window, int n_chunks) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int64_t t = r / n_heads;
+    const int h = int(r - t * n_heads);
+    const int sg = token_seg[t];
+    if (single_only && single_only[sg + 1] - single_only[sg] > 1) return;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n = min(n_chunks, pos / KC - lo / KC + 1);
+    const float* mine = parts + r * n_chunks * int64_t(dv + 2);
+    float m = sink ? sink[h] : -INFINITY;
+    for (int i = 0; i < n; i++) m = fmaxf(m, mine[i * int64_t(dv + 2)]);
+    float l = sink ? expf(sink[h] - m) : 0.0f;
+    for (int i = 0; i < n; i++) l += mine[i * int64_t(dv + 2) + 1] * expf(mine[i * int64_t(dv + 2)] - m);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    for (int c = lane; c < dv; c += 32) {
+        float o = 0.0f;
+        for (int i = 0; i < n; i++) o = fmaf(mine[i * int64_t(dv + 2) + 2 + c], expf(mine[i * int64_t(dv + 2)] - m), o);
+        out[r * dv + c] = ib::from_f32<T>(o * inv);
     }
 }
 
@@ -401,41 +624,161 @@ __global__ void tail_update_kernel(const float* __restrict__ rows, int64_t ld, i
 // beta at aux_col + H + h, k.q at aux_col + 2 H + h / heads_per_qk. raw_out [tokens, H, dv] float.
 constexpr int LK = 8;
 
+__device__ __forceinline__ void copy_async16(float* smem_dst, const float* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void copy_async4(float* smem_dst, const float* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(uint32_t(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src) : "memory");
+}
+
+// One token's operands of a thread: its R rows of q, k (and of the decays), the value of its column, the scalars.
+template <int R, int MODE>
+struct ScanOperands {
+    float4 q[R / 4], k[R / 4], a[MODE == 0 ? R / 4 : 1];
+    float v, g, beta, kq;
+    __device__ __forceinline__ void load(const float* qs, const float* ks, const float* as, const float* vs, int c, int dpp, int off,
+                                         int cb, int col_l) {
+        const float4* q4 = reinterpret_cast<const float4*>(qs + c * dpp + off);
+        const float4* k4 = reinterpret_cast<const float4*>(ks + c * dpp + off);
+#pragma unroll
+        for (int i = 0; i < R / 4; i++) { q[i] = q4[i]; k[i] = k4[i]; }
+        if (MODE == 0) {
+            const float4* a4 = reinterpret_cast<const float4*>(as + c * dpp + off);
+#pragma unroll
+            for (int i = 0; i < R / 4; i++) a[i] = a4[i];
+        } else {
+            g = as[c * 4 + 0]; beta = as[c * 4 + 1]; kq = as[c * 4 + 2];
+        }
+        v = vs[c * cb + col_l];
+    }
+};
+
+// One token through a thread's share of the state; returns the column's read-out (valid in every lane of its group).
+template <int R, int MODE>
+__device__ __forceinline__ float scan_token(float (&S)[R], const ScanOperands<R, MODE>& x) {
+    const float v = x.v;
+    if (MODE == 0) {
+        float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+        for (int i4 = 0; i4 < R / 4; i4++) {
+            const float4 a = x.a[i4], k = x.k[i4], q = x.q[i4];
+            S[4 * i4 + 0] = fmaf(a.x, S[4 * i4 + 0], k.x * v);
+            S[4 * i4 + 1] = fmaf(a.y, S[4 * i4 + 1], k.y * v);
+            S[4 * i4 + 2] = fmaf(a.z, S[4 * i4 + 2], k.z * v);
+            S[4 * i4 + 3] = fmaf(a.w, S[4 * i4 + 3], k.w * v);
+            p0 = fmaf(S[4 * i4 + 0], q.x, p0);
+            p1 = fmaf(S[4 * i4 + 1], q.y, p1);
+            p2 = fmaf(S[4 * i4 + 2], q.z, p2);
+            p3 = fmaf(S[4 * i4 + 3], q.w, p3);
+        }
+        float p = (p0 + p1) + (p2 + p3);
+        p += __shfl_xor_sync(0xffffffffu, p, 1);
+        p += __shfl_xor_sync(0xffffffffu, p, 2);
+        p += __shfl_xor_sync(0xffffffffu, p, 4);
+        return p;
+    }
+    const float g = x.g;
+    float r0 = 0.0f, r1 = 0.0f, p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+    for (int i4 = 0; i4 < R / 4; i4++) {
+        const float4 k = x.k[i4], q = x.q[i4];
+        r0 = fmaf(S[4 * i4 + 0], k.x, r0);
+        r1 = fmaf(S[4 * i4 + 1], k.y, r1);
+        r0 = fmaf(S[4 * i4 + 2], k.z, r0);
+        r1 = fmaf(S[4 * i4 + 3], k.w, r1);
+        p0 = fmaf(S[4 * i4 + 0], q.x, p0);
+        p1 = fmaf(S[4 * i4 + 1], q.y, p1);
+        p0 = fmaf(S[4 * i4 + 2], q.z, p0);
+        p1 = fmaf(S[4 * i4 + 3], q.w, p1);
+    }
+    float r = r0 + r1, p = p0 + p1;
+    r += __shfl_xor_sync(0xffffffffu, r, 1);
+    p += __shfl_xor_sync(0xffffffffu, p, 1);
+    r += __shfl_xor_sync(0xffffffffu, r, 2);
+    p += __shfl_xor_sync(0xffffffffu, p, 2);
+    r += __shfl_xor_sync(0xffffffffu, r, 4);
+    p += __shfl_xor_sync(0xffffffffu, p, 4);
+    const float u = x.beta * (v - g * r);
+#pragma unroll
+    for (int i4 = 0; i4 < R / 4; i4++) {
+        const float4 k = x.k[i4];
+        S[4 * i4 + 0] = fmaf(k.x, u, g * S[4 * i4 + 0]);
+        S[4 * i4 + 1] = fmaf(k.y, u, g * S[4 * i4 + 1]);
+        S[4 * i4 + 2] = fmaf(k.z, u, g * S[4 * i4 + 2]);
+        S[4 * i4 + 3] = fmaf(k.w, u, g * S[4 * i4 + 3]);
+    }
+    return fmaf(u, x.kq, g * p);
+}
+
+// Staging: a token's q, k (and decays) lie in shared memory as [lane group][R + 4] (the four floats of padding keep
+// the eight lanes' 16-byte loads on different banks), rows beyond d zero. With `pipelined` (every row, column offset
+// and size a multiple of four floats) the rows are copied as they lie by asynchronous 16-byte copies, one chunk ahead
+// of the one being computed; otherwise element by element. The operands of token c + 1 are read into registers while
+// token c is computed. The arithmetic per token is the same in every case.
 template <int R, int MODE>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_col, int v_col,
                   const float* __restrict__ aux, int64_t lda, int aux_col, float* __restrict__ state,
                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ raw_out,
-                  int n_heads, int heads_per_qk, int d, int dv, int cb, int chunk, int write_state) {
-    ib::pdl_wait();
+                  int n_heads, int heads_per_qk, int d, int dv, int cb, int chunk, int write_state, int pipelined) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int DP = LK * R;
-    float* qs = sm;                          // [chunk][DP]
-    float* ks = qs + chunk * DP;             // [chunk][DP]
-    float* as = ks + chunk * DP;             // MODE 0: [chunk][DP] decays; MODE 1: [chunk][4] g, beta, k.q
-    float* vs = as + chunk * (MODE == 0 ? DP : 4);   // [chunk][cb]
+    constexpr int RP = R + 4, DPP = LK * RP;
+    const int n_buf = pipelined ? 2 : 1;
+    const int a_tok = MODE == 0 ? DPP : 4;
+    float* qs = sm;                          // [n_buf][chunk][DPP]
+    float* ks = qs + n_buf * chunk * DPP;
+    float* as = ks + n_buf * chunk * DPP;    // MODE 0: [n_buf][chunk][DPP] decays; MODE 1: [n_buf][chunk][4] g, beta, k.q
+    float* vs = as + n_buf * chunk * a_tok;  // [n_buf][chunk][cb]
+    const int total = n_buf * chunk * (2 * DPP + a_tok + cb);
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int hq = h / heads_per_qk;
     const int lk = tid & (LK - 1), col_l = tid >> 3;
-    const int col = blockIdx.z * cb + col_l;
+    const int col0 = blockIdx.z * cb, col = col0 + col_l;
     const bool live = col < dv;
-    const int k0 = lk * R;
+    const int k0 = lk * R, off = lk * RP;
+    for (int i = tid; i < total; i += blockDim.x) sm[i] = 0.0f;       // padding and rows beyond d stay zero
+    ib::pdl_wait();
     const int64_t t0 = seg_start[s];
     const int len = int(seg_start[s + 1] - t0);
     float* S_g = state + (int64_t(seg_slot[s]) * n_heads + h) * int64_t(d) * dv;
     float S[R];
 #pragma unroll
     for (int i = 0; i < R; i++) S[i] = (live && k0 + i < d) ? S_g[int64_t(k0 + i) * dv + col] : 0.0f;
+    __syncthreads();
 
-    for (int c0 = 0; c0 < len; c0 += chunk) {
+    auto request = [&](int c0, int b) {      // asynchronous copies of the chunk that starts at token c0 into buffer b
         const int n = min(chunk, len - c0);
-        __syncthreads();                     // the last chunk's values have been read
-        for (int idx = tid; idx < n * DP; idx += blockDim.x) {
-            const int c = idx / DP, j = idx - c * DP;
+        const int d4 = d / 4, cb4 = cb / 4;
+        for (int idx = tid; idx < n * d4; idx += blockDim.x) {
+            const int c = idx / d4, j = (idx - c * d4) * 4;
+            const int dst = (b * chunk + c) * DPP + (j / R) * RP + j % R;
             const float* row = rows + (t0 + c0 + c) * ld;
-            qs[idx] = j < d ? row[q_col + hq * d + j] : 0.0f;
-            ks[idx] = j < d ? row[k_col + hq * d + j] : 0.0f;
-            if (MODE == 0) as[idx] = j < d ? aux[(t0 + c0 + c) * lda + aux_col + h * d + j] : 0.0f;
+            copy_async16(qs + dst, row + q_col + hq * d + j);
+            copy_async16(ks + dst, row + k_col + hq * d + j);
+            if (MODE == 0) copy_async16(as + dst, aux + (t0 + c0 + c) * lda + aux_col + h * d + j);
+        }
+        if (MODE == 1) {
+            for (int idx = tid; idx < n * 3; idx += blockDim.x) {
+                const int c = idx / 3, e = idx - c * 3;
+                const float* ar = aux + (t0 + c0 + c) * lda + aux_col;
+                copy_async4(as + (b * chunk + c) * 4 + e, ar + (e == 0 ? h : (e == 1 ? n_heads + h : 2 * n_heads + hq)));
+            }
+        }
+        for (int idx = tid; idx < n * cb4; idx += blockDim.x) {
+            const int c = idx / cb4, j = (idx - c * cb4) * 4;
+            if (col0 + j < dv) copy_async16(vs + (b * chunk + c) * cb + j, rows + (t0 + c0 + c) * ld + v_col + h * dv + col0 + j);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto stage = [&](int c0) {               // the same chunk element by element (any sizes and offsets)
+        const int n = min(chunk, len - c0);
+        for (int idx = tid; idx < n * d; idx += blockDim.x) {
+            const int c = idx / d, j = idx - c * d;
+            const int dst = c * DPP + (j / R) * RP + j % R;
+            const float* row = rows + (t0 + c0 + c) * ld;
+            qs[dst] = row[q_col + hq * d + j];
+            ks[dst] = row[k_col + hq * d + j];
+            if (MODE == 0) as[dst] = aux[(t0 + c0 + c) * lda + aux_col + h * d + j];
         }
         if (MODE == 1) {
             for (int c = tid; c < n; c += blockDim.x) {
@@ -446,70 +789,40 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
             }
         }
         for (int idx = tid; idx < n * cb; idx += blockDim.x) {
-            const int c = idx / cb, j = blockIdx.z * cb + (idx - c * cb);
+            const int c = idx / cb, j = col0 + (idx - c * cb);
             vs[idx] = j < dv ? rows[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
         }
-        __syncthreads();
-        for (int c = 0; c < n; c++) {
-            const float v = vs[c * cb + col_l];
-            const float4* q4 = reinterpret_cast<const float4*>(qs + c * DP + k0);
-            const float4* k4 = reinterpret_cast<const float4*>(ks + c * DP + k0);
-            float o;
-            if (MODE == 0) {
-                const float4* a4 = reinterpret_cast<const float4*>(as + c * DP + k0);
-                float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
-#pragma unroll
-                for (int i4 = 0; i4 < R / 4; i4++) {
-                    const float4 a = a4[i4], k = k4[i4], q = q4[i4];
-                    S[4 * i4 + 0] = fmaf(a.x, S[4 * i4 + 0], k.x * v);
-                    S[4 * i4 + 1] = fmaf(a.y, S[4 * i4 + 1], k.y * v);
-                    S[4 * i4 + 2] = fmaf(a.z, S[4 * i4 + 2], k.z * v);
-                    S[4 * i4 + 3] = fmaf(a.w, S[4 * i4 + 3], k.w * v);
-                    p0 = fmaf(S[4 * i4 + 0], q.x, p0);
-                    p1 = fmaf(S[4 * i4 + 1], q.y, p1);
-                    p2 = fmaf(S[4 * i4 + 2], q.z, p2);
-                    p3 = fmaf(S[4 * i4 + 3], q.w, p3);
-                }
-                float p = (p0 + p1) + (p2 + p3);
-                p += __shfl_xor_sync(0xffffffffu, p, 1);
-                p += __shfl_xor_sync(0xffffffffu, p, 2);
-                p += __shfl_xor_sync(0xffffffffu, p, 4);
-                o = p;
+    };
+
+    if (pipelined && len > 0) request(0, 0);
+    int b = 0;
+    for (int c0 = 0; c0 < len; c0 += chunk) {
+        const int n = min(chunk, len - c0);
+        if (pipelined) {
+            if (c0 + chunk < len) {
+                request(c0 + chunk, b ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
             } else {
-                const float g = as[c * 4 + 0], beta = as[c * 4 + 1], kq = as[c * 4 + 2];
-                float r0 = 0.0f, r1 = 0.0f, p0 = 0.0f, p1 = 0.0f;
-#pragma unroll
-                for (int i4 = 0; i4 < R / 4; i4++) {
-                    const float4 k = k4[i4], q = q4[i4];
-                    r0 = fmaf(S[4 * i4 + 0], k.x, r0);
-                    r1 = fmaf(S[4 * i4 + 1], k.y, r1);
-                    r0 = fmaf(S[4 * i4 + 2], k.z, r0);
-                    r1 = fmaf(S[4 * i4 + 3], k.w, r1);
-                    p0 = fmaf(S[4 * i4 + 0], q.x, p0);
-                    p1 = fmaf(S[4 * i4 + 1], q.y, p1);
-                    p0 = fmaf(S[4 * i4 + 2], q.z, p0);
-                    p1 = fmaf(S[4 * i4 + 3], q.w, p1);
-                }
-                float r = r0 + r1, p = p0 + p1;
-                r += __shfl_xor_sync(0xffffffffu, r, 1);
-                p += __shfl_xor_sync(0xffffffffu, p, 1);
-                r += __shfl_xor_sync(0xffffffffu, r, 2);
-                p += __shfl_xor_sync(0xffffffffu, p, 2);
-                r += __shfl_xor_sync(0xffffffffu, r, 4);
-                p += __shfl_xor_sync(0xffffffffu, p, 4);
-                const float u = beta * (v - g * r);
-                o = fmaf(u, kq, g * p);
-#pragma unroll
-                for (int i4 = 0; i4 < R / 4; i4++) {
-                    const float4 k = k4[i4];
-                    S[4 * i4 + 0] = fmaf(k.x, u, g * S[4 * i4 + 0]);
-                    S[4 * i4 + 1] = fmaf(k.y, u, g * S[4 * i4 + 1]);
-                    S[4 * i4 + 2] = fmaf(k.z, u, g * S[4 * i4 + 2]);
-                    S[4 * i4 + 3] = fmaf(k.w, u, g * S[4 * i4 + 3]);
-                }
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
             }
-            if (lk == 0 && live) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + col] = o;
+        } else {
+            stage(c0);
         }
+        __syncthreads();                     // the chunk has arrived
+        const float* qb = qs + b * chunk * DPP;
+        const float* kb = ks + b * chunk * DPP;
+        const float* ab = as + b * chunk * a_tok;
+        const float* vb = vs + b * chunk * cb;
+        ScanOperands<R, MODE> cur, nxt;
+        cur.load(qb, kb, ab, vb, 0, DPP, off, cb, col_l);
+        for (int c = 0; c < n; c++) {
+            if (c + 1 < n) nxt.load(qb, kb, ab, vb, c + 1, DPP, off, cb, col_l);
+            const float o = scan_token<R, MODE>(S, cur);
+            if (lk == 0 && live) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + col] = o;
+            cur = nxt;
+        }
+        __syncthreads();                     // every thread has read this buffer: the copies after next may fill it
+        if (pipelined) b ^= 1;
     }
     if (write_state && live) {
 #pragma unroll
@@ -592,6 +905,11 @@ IB_EXPORT int ib_glu_act(const void* rows, int64_t ld, int64_t gate_col, int64_t
     if (dtype == IB_F32)
         IB_LAUNCH(glu_act_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)rows, ld, gate_col, up_col, width, kind, limit,
                   limit2, slope, scale, group, n_groups, (float*)out, n);
+    else if (dtype == IB_BF16 && width % 8 == 0 && ld % 8 == 0 && gate_col % 8 == 0 && up_col % 8 == 0 && group % 8 == 0 &&
+             !((uintptr_t(rows) | uintptr_t(out)) & 15))
+        // (chosen by sizes and addresses, never by the number of rows)
+        IB_LAUNCH(glu_act_vec_kernel, blocks_for(n / 8, 256), 256, 0, (const bf16*)rows, ld, gate_col, up_col, width / 8, kind, limit,
+                  limit2, slope, scale, group, n_groups, (bf16*)out, n / 8);
     else if (dtype == IB_BF16)
         IB_LAUNCH(glu_act_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)rows, ld, gate_col, up_col, width, kind, limit,
                   limit2, slope, scale, group, n_groups, (bf16*)out, n);
@@ -627,6 +945,52 @@ IB_EXPORT int ib_rownorm_store(const void* rows, int64_t ld, int col0, const flo
     else
         return ib::fail(IB_ERR_ARG, "ib_rownorm_store: unknown dtype %d", dtype);
     return ib::check_launch("ib_rownorm_store");
+}
+
+// Floats of workspace that ib_attention_split needs for n_tokens tokens whose queries see up to `visible` keys.
+IB_EXPORT int64_t ib_attention_split_workspace(int64_t n_tokens, int n_heads, int dv, int visible) {
+    const int64_t n_chunks = (visible + KC - 1) / KC + 1;
+    return n_tokens * n_heads * n_chunks * (dv + 2);
+}
+
+// q, out [tokens, heads * d / dv]; caches [pages, kv heads, page_size, d / dv]; `visible`: the most keys a query of the
+// step sees (its window, or the longest context); workspace as ib_attention_split_workspace says.
+IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int64_t max_blocks,
+                                 const int* token_seg, const int* positions, const int* single_only, void* out, float* workspace,
+                                 int64_t n_tokens, int n_heads, int n_kv, int d, int dv, int page_size, int window, float scale,
+                                 int64_t n_pages, const float* dist_bias, int bias_len, const float* sink, int visible, int dtype,
+                                 int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_kv <= 0 || n_heads % n_kv || n_heads / n_kv > GMAX)
+        return ib::fail(IB_ERR_ARG, "ib_attention_split: %d heads on %d kv heads (groups of up to %d)", n_heads, n_kv, GMAX);
+    if (d <= 0 || dv <= 0 || d > 512 || dv > 1024 || page_size <= 0 || visible <= 0 || !workspace)
+        return ib::fail(IB_ERR_ARG, "ib_attention_split: bad sizes");
+    if (dist_bias && bias_len <= 0) return ib::fail(IB_ERR_ARG, "ib_attention_split: a distance bias needs at least one row");
+    const int n_chunks = (visible + KC - 1) / KC + 1;
+    if (n_kv > 65535 || n_chunks > 65535) return ib::fail(IB_ERR_ARG, "ib_attention_split: too many kv heads or chunks");
+    const int group = n_heads / n_kv;
+    const size_t smem = size_t(group * ((d + 3) & ~3) + group * KC + 2 * GMAX) * sizeof(float) + KC * sizeof(int64_t);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_attention_split: %d heads of %d do not fit", group, d);
+    const dim3 grid{unsigned(n_tokens), unsigned(n_kv), unsigned(n_chunks)};
+    const int64_t rows = n_tokens * n_heads;
+    if (dtype == IB_F32) {
+        const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
+        IB_LAUNCH(split_attention_kernel<float>, grid, KC, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table,
+                  max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,
+                  dist_bias, bias_len, n_chunks, vec, status);
+        IB_LAUNCH(split_attention_merge_kernel<float>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
+                  (float*)out, rows, n_heads, dv, window, n_chunks);
+    } else if (dtype == IB_BF16) {
+        const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
+        IB_LAUNCH(split_attention_kernel<bf16>, grid, KC, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+                  max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,
+                  dist_bias, bias_len, n_chunks, vec, status);
+        IB_LAUNCH(split_attention_merge_kernel<bf16>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
+                  (bf16*)out, rows, n_heads, dv, window, n_chunks);
+    } else {
+        return ib::fail(IB_ERR_ARG, "ib_attention_split: unknown dtype %d", dtype);
+    }
+    return ib::check_launch("ib_attention_split");
 }
 
 IB_EXPORT int ib_decay_gates(float* rows, int64_t ld, int q_col, int low_col, int rank, const float* up, const float* bias,
@@ -671,9 +1035,10 @@ IB_EXPORT int ib_state_scan_max_dim() { return LK * 32; }
 template <int R, int MODE>
 static int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* rows, int64_t ld, int q_col,
                        int k_col, int v_col, const float* aux, int64_t lda, int aux_col, float* state, const int* seg_start,
-                       const int* seg_slot, float* raw_out, int n_heads, int hpq, int d, int dv, int cb, int chunk, int write_state) {
+                       const int* seg_slot, float* raw_out, int n_heads, int hpq, int d, int dv, int cb, int chunk, int write_state,
+                       int pipelined) {
     IB_LAUNCH((state_scan_kernel<R, MODE>), grid, threads, smem, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start,
-              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state);
+              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state, pipelined);
     return ib::check_launch("ib_state_scan");
 }
 
@@ -694,16 +1059,22 @@ IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, 
         const int sms = sm_count > 0 ? sm_count : 148;
         while (cb > 8 && n_segments * n_heads * ((dv + cb / 2 - 1) / (cb / 2)) <= sms) cb /= 2;
     }
-    const int dp = LK * r;
-    const int per_token = 2 * dp + (mode == 0 ? dp : 4) + cb;
-    int chunk = 11264 / per_token;
+    // asynchronous copies of rows as they lie need every offset and size on 16 bytes; prompt portions only (a step of
+    // single tokens has nothing to copy ahead)
+    const int pipelined = spread && d % 4 == 0 && dv % 4 == 0 && cb % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 &&
+                          v_col % 4 == 0 && (mode != 0 || (lda % 4 == 0 && aux_col % 4 == 0 && !(uintptr_t(aux) & 15))) &&
+                          !(uintptr_t(rows) & 15);
+    const int dpp = LK * (r + 4), n_buf = pipelined ? 2 : 1;
+    const int per_token = 2 * dpp + (mode == 0 ? dpp : 4) + cb;
+    int chunk = 11264 / (n_buf * per_token);
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
-    const size_t smem = size_t(chunk) * per_token * sizeof(float);
+    const size_t smem = size_t(n_buf) * chunk * per_token * sizeof(float);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_state_scan: a token of %d floats does not fit the staging area", per_token);
     const dim3 grid{unsigned(n_segments), unsigned(n_heads), unsigned((dv + cb - 1) / cb)};
     const int threads = cb * LK;
 #define IB_SCAN(RR, MM)                                                                                                          \
     return launch_scan<RR, MM>(grid, threads, smem, stream, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start, \
-                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state)
+                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state, pipelined)
     if (mode == 0) {
         if (r == 4) IB_SCAN(4, 0);
         if (r == 8) IB_SCAN(8, 0);

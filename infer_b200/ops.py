@@ -587,23 +587,66 @@ def rownorm_store(rows: torch.Tensor, col0: int, wq: Optional[torch.Tensor], wk:
     return q
 
 
+def attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
+                    dist_bias=None, sink=None, out=None, single_only=False):
+    """Paged attention with keys split over CTAs (chunks of 128 keys aligned to absolute positions, merged in
+    ascending order), for tokens that read a few hundred keys each: decoded tokens of a windowed layer. Takes a
+    distance bias float32 [L, heads] and a sink float32 [heads]. With ``single_only`` only tokens that are a segment
+    of their own are computed (into ``out``, whose other rows stay)."""
+    _check(q, "q")
+    T = q.shape[0]
+    n_pages, ckv, page_size, chd = k_cache.shape
+    _check(q, "q", None, (T, n_heads * head_dim))
+    _check(k_cache, "k_cache", q.dtype, (n_pages, n_kv, page_size, head_dim))
+    _check(v_cache, "v_cache", q.dtype, (n_pages, n_kv, page_size, v_head_dim))
+    if dist_bias is not None:
+        _check(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != n_heads:
+            raise KernelError(f"dist_bias must be [distances, {n_heads}], got {tuple(dist_bias.shape)}")
+    if sink is not None:
+        _check(sink, "sink", torch.float32, (n_heads,))
+    if out is None:
+        out = torch.empty((T, n_heads * v_head_dim), dtype=q.dtype, device=q.device)
+    else:
+        _check(out, "out", q.dtype, (T, n_heads * v_head_dim))
+    visible = min(int(window), int(step.max_ctx_len)) if window else int(step.max_ctx_len)
+    visible = max(visible, 1)
+    n_ws = int(_fn("mix", "ib_attention_split_workspace", [c_int64, c_int, c_int, c_int], restype=c_int64)(T, n_heads, v_head_dim, visible))
+    ws = torch.empty(n_ws, dtype=torch.float32, device=q.device)
+    f = _fn("mix", "ib_attention_split", [c_void_p] * 4 + [c_int64] + [c_void_p] * 5 + [c_int64] + [c_int] * 6 + [c_float, c_int64,
+                                          c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+          step.token_seg.data_ptr(), step.positions.data_ptr(), step.seg_start.data_ptr() if single_only else None, out.data_ptr(),
+          ws.data_ptr(), T, n_heads, n_kv, head_dim, v_head_dim, page_size, int(window or 0), float(scale), n_pages,
+          _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink), visible, dtype_code(q.dtype),
+          _ptr(step.status), _stream())
+    return out
+
+
+ATTENTION_SPLIT_GROUP_MAX = 16
+
+
 def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
                      dist_bias, sink, dist_bias_by_head=None):
-    """Attention with a distance bias and a sink on the tensor-core kernel for prompt portions, where it takes the
-    shape (bfloat16, keys and values of one size that the kernel is built for, a step that has portions); one-token
-    segments of the same step go through the plain kernel into the same rows. None where the shape is refused (the
-    caller then uses the plain kernel for everything). ``dist_bias_by_head``: float32 [heads, L], the bias divided
-    by the scale."""
+    """Attention with a distance bias and a sink on the faster kernels, where they take the shape: prompt portions on
+    the tensor-core kernel (bfloat16, keys and values of one size that the kernel is built for), one-token segments
+    on the kernel that splits a token's keys over CTAs, into the same rows. None where a shape is refused (the caller
+    then uses the plain kernel for everything). ``dist_bias_by_head``: float32 [heads, L], the bias divided by the
+    scale."""
     from . import fast_ops
-    if step.max_q_len <= 1 or v_head_dim != head_dim or (dist_bias is not None and dist_bias_by_head is None):
+    if n_heads // n_kv > ATTENTION_SPLIT_GROUP_MAX:
+        return None
+    if step.max_q_len <= 1:
+        return attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink)
+    if v_head_dim != head_dim or (dist_bias is not None and dist_bias_by_head is None):
         return None
     out = fast_ops.attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, window, scale,
                                             dist_bias_by_head, sink)
     if out is None:
         return None
     if any(n == 1 for n in step.seg_lens):
-        attention_plain(q, k_cache, v_cache, block_table, step.token_seg, step.positions, n_heads, n_kv, head_dim, window, scale,
-                        step.status, v_head_dim, dist_bias, sink, out, step.seg_start)
+        attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink,
+                        out, single_only=True)
     return out
 
 

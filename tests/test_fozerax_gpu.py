@@ -177,8 +177,9 @@ def test_the_design_runs_on_its_own_kernels():
                  "ib_dual_norm_sum", "ib_head_norm_gate"):
         assert ran.get(kind, 0) >= 2, (kind, ran)
     assert ran.get("ib_gemm_tc", 0) >= 1                     # the tensor-core product serves the prompt's matrices
-    # keys and values of 64: the prompt's attention runs on the tensor-core kernel, the decoded token's on the plain one
-    assert ran.get("ib_attention_prefill_tc_biased", 0) == 1 and ran.get("ib_attention_plain", 0) == 1
+    # keys and values of 64: the prompt's attention runs on the tensor-core kernel, the decoded token's on the kernel
+    # that splits its keys over CTAs, none on the plain one
+    assert ran.get("ib_attention_prefill_tc_biased", 0) == 1 and ran.get("ib_attention_split", 0) == 1 and "ib_attention_plain" not in ran
 
 
 # ----------------------------------------------------------------------------------------------- generation, programs

@@ -46,13 +46,15 @@ def test_two_normalised_sides_and_the_layer_norm_in_one_pass(width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-def test_gated_activations(dtype):
+@pytest.mark.parametrize("sizes", [(3, 5, 7, 2), (3, 16, 24, 8)], ids=["odd", "by-eights"])
+def test_gated_activations(dtype, sizes):
     g = torch.Generator().manual_seed(3)
-    T, E, ff, fs = 9, 3, 5, 7
+    T = 9
+    E, ff, fs, c0 = sizes
     width = E * ff + fs
-    rows = (3.0 * torch.randn(T, 2 + 2 * width, generator=g)).to(dtype)
-    gate, up = rows[:, 2:2 + width].double(), rows[:, 2 + width:].double()
-    got = ops.glu_act(rows.to(DEV), 2, 2 + width, width, "gelu_tanh").double().cpu()
+    rows = (3.0 * torch.randn(T, c0 + 2 * width, generator=g)).to(dtype)
+    gate, up = rows[:, c0:c0 + width].double(), rows[:, c0 + width:].double()
+    got = ops.glu_act(rows.to(DEV), c0, c0 + width, width, "gelu_tanh").double().cpu()
     assert torch.allclose(got, pf.gelu_tanh(gate) * up, **_tol(dtype))
     scale = torch.rand(T, E, generator=g)
     scale[:, 1] = 0.0
@@ -63,7 +65,7 @@ def test_gated_activations(dtype):
         return gv * torch.sigmoid(pf.EXPERT_SLOPE * gv) * (uv + 1.0)
     want = torch.cat([expert(gate[:, :E * ff], up[:, :E * ff], lim) * scale.double().repeat_interleave(ff, dim=1),
                       expert(gate[:, E * ff:], up[:, E * ff:], lim2)], dim=1)
-    got = ops.glu_act(rows.to(DEV), 2, 2 + width, width, "clipped_swish", lim, lim2, pf.EXPERT_SLOPE, scale.to(DEV), ff, E).double().cpu()
+    got = ops.glu_act(rows.to(DEV), c0, c0 + width, width, "clipped_swish", lim, lim2, pf.EXPERT_SLOPE, scale.to(DEV), ff, E).double().cpu()
     assert torch.allclose(got, want, **_tol(dtype))
     assert float(got[:, ff:2 * ff].abs().sum()) == 0.0
 
@@ -230,6 +232,49 @@ def test_tensor_core_attention_with_distance_bias_and_sink(sizes, window):
     ref = torch.cat([want[0][first:], want[1][m - 1:]])
     assert torch.allclose(got, ref, rtol=3e-2, atol=3e-2)
     assert float((got - ref).pow(2).mean().sqrt()) < 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("window", [None, 5, 72, 128, 300])
+@pytest.mark.parametrize("sizes", [(6, 2, 64, 48), (3, 3, 10, 7), (16, 1, 128, 128), (4, 2, 24, 40)])
+def test_single_tokens_with_their_keys_split_over_ctas(sizes, window, dtype):
+    """Decoded tokens at positions around chunk borders (multiples of 128), page borders and the first positions; one
+    key at each edge of the window stands out; a longer segment in the same step is left alone."""
+    from infer_b200.parts.attention import distance_bias_table
+    H, G, d, dv = sizes
+    B, D, scale = 12, 40.0, 0.2
+    g = torch.Generator().manual_seed(d + (window or 0))
+    n = 420
+    q = torch.randn(n, H, d, generator=g).to(dtype).double()
+    k = torch.randn(n, G, d, generator=g).to(dtype).double()
+    v = torch.randn(n, G, dv, generator=g).to(dtype).double()
+    rel, sink = torch.randn(B, H, generator=g), torch.randn(H, generator=g)
+    probes = [0, 1, 15, 16, 127, 128, 129, 255, 256, 300, 383, 384, 419]
+    if window is not None:
+        for pr_ in probes:
+            if pr_ - window >= 0:
+                k[pr_ - (window - 1), 0] += 2.0 * q[pr_, 0] / q[pr_, 0].norm() * math.sqrt(d)
+                k[pr_ - window, G - 1] += 2.0 * q[pr_, H - 1] / q[pr_, H - 1].norm() * math.sqrt(d)
+        k = k.to(dtype).double()
+    want = _biased_attention(q, k, v, rel, sink, B, D, window, scale)
+    table_row = list(np.random.default_rng(1).permutation(30))[:27]
+    kc, vc = _paged([k], [v], [table_row], 30, G, d, dv, dtype)
+    # every probe is a request of its own that shares the pages (one row of the table each), plus one longer segment
+    S = len(probes) + 1
+    table = torch.tensor([table_row] * S, dtype=torch.int32, device=DEV)
+    step = _Step([1] * len(probes) + [3], probes + [200], list(range(S)))
+    step.seg_lens, step.max_q_len, step.max_ctx_len = step.lens, 3, n
+    rows = torch.cat([q[probes], q[200:203]]).reshape(-1, H * d).to(dtype).to(DEV).contiguous()
+    bias = distance_bias_table(rel, D, window).to(DEV)
+    out = torch.full((rows.shape[0], H * dv), 7.0, dtype=dtype, device=DEV)
+    ops.attention_split(rows, kc.to(DEV), vc.to(DEV), table, step, H, G, d, dv, window, scale, bias, sink.to(DEV), out, single_only=True)
+    got = out.double().cpu().view(-1, H, dv)
+    assert torch.allclose(got[:len(probes)], want[probes], **_tol(dtype))
+    assert float((got[len(probes):] - 7.0).abs().sum()) == 0.0               # the longer segment's rows were left alone
+    step.max_q_len = 1
+    every = ops.attention_split(rows, kc.to(DEV), vc.to(DEV), table, step, H, G, d, dv, window, scale, bias, sink.to(DEV))
+    assert torch.allclose(every.double().cpu().view(-1, H, dv)[len(probes):], want[200:203], **_tol(dtype))
+    assert int(step.status.item()) == 0
 
 
 @pytest.mark.parametrize("sizes", [(2, 16, 4), (1, 40, 3), (3, 128, 16)])
