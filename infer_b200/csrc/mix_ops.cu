@@ -307,6 +307,7 @@ rownorm_store_kernel(const T* __restrict__ rows, int64_t ld, int col0, const flo
 // only. `single_only` (a step's seg_start): tokens of longer segments are skipped (another kernel's).
 constexpr int KC = 128;
 constexpr int GMAX = 16;
+constexpr int VT = 32;                 // value rows staged at a time
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&x)[8]);
@@ -333,7 +334,7 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
                        const int* __restrict__ positions, const int* __restrict__ single_only, float* __restrict__ parts,
                        int n_heads, int n_kv, int d, int dv, int page_size, int window, float scale, int64_t n_pages,
-                       const float* __restrict__ dist_bias, int bias_len, int n_chunks, int vec, int* status) {
+                       const float* __restrict__ dist_bias, int bias_len, int n_chunks, int vec, int vec_v, int* status) {
     ib::pdl_wait();
     const int64_t t = blockIdx.x;
     const int g = blockIdx.y, ci = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -373,18 +374,28 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
             rowoff[tid] = row;
             const T* kr = k_cache + row * d;
             if (vec) {
-                for (int e = 0; e < d; e += 8) {
-                    float kv[8];
-                    load8<T>(kr + e, kv);
+                // four 16-byte loads of the row are in flight together (a thread's row is its own: nothing is shared)
+                for (int e0 = 0; e0 < d; e0 += 32) {
+                    float kv[4][8];
 #pragma unroll
-                    for (int gq = 0; gq < GMAX; gq++) {
-                        if (gq < group) {
-                            const float4 a = *reinterpret_cast<const float4*>(qs + gq * dq + e);
-                            const float4 b = *reinterpret_cast<const float4*>(qs + gq * dq + e + 4);
-                            float x = acc[gq];
-                            x = fmaf(a.x, kv[0], x); x = fmaf(a.y, kv[1], x); x = fmaf(a.z, kv[2], x); x = fmaf(a.w, kv[3], x);
-                            x = fmaf(b.x, kv[4], x); x = fmaf(b.y, kv[5], x); x = fmaf(b.z, kv[6], x); x = fmaf(b.w, kv[7], x);
-                            acc[gq] = x;
+                    for (int b4 = 0; b4 < 4; b4++) {
+                        if (e0 + 8 * b4 < d) load8<T>(kr + e0 + 8 * b4, kv[b4]);
+                    }
+#pragma unroll
+                    for (int b4 = 0; b4 < 4; b4++) {
+                        const int e = e0 + 8 * b4;
+                        if (e < d) {
+#pragma unroll
+                            for (int gq = 0; gq < GMAX; gq++) {
+                                if (gq < group) {
+                                    const float4 a = *reinterpret_cast<const float4*>(qs + gq * dq + e);
+                                    const float4 b = *reinterpret_cast<const float4*>(qs + gq * dq + e + 4);
+                                    float x = acc[gq];
+                                    x = fmaf(a.x, kv[b4][0], x); x = fmaf(a.y, kv[b4][1], x); x = fmaf(a.z, kv[b4][2], x); x = fmaf(a.w, kv[b4][3], x);
+                                    x = fmaf(b.x, kv[b4][4], x); x = fmaf(b.y, kv[b4][5], x); x = fmaf(b.z, kv[b4][6], x); x = fmaf(b.w, kv[b4][7], x);
+                                    acc[gq] = x;
+                                }
+                            }
                         }
                     }
                 }
@@ -428,20 +439,61 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     }
     __syncthreads();
     const int j0 = max(lo, base) - base, j1 = min(pos, base + KC - 1) - base;
-    for (int c = tid; c < dv; c += KC) {
-        float o[GMAX];
+    if (vec_v) {
+        // Value rows reach shared memory VT keys at a time, by 16-byte loads that all threads issue together; then a
+        // thread per channel adds them in ascending key order (the same order as the loop below).
+        T* vt = reinterpret_cast<T*>(rowoff + KC);           // [VT][dv]
+        constexpr int PER = 16 / int(sizeof(T));             // values per 16-byte load
+        const int n_c = (dv + KC - 1) / KC;                  // channel passes of a thread (dv <= 2 KC)
+        float o0[GMAX], o1[GMAX];
 #pragma unroll
-        for (int gq = 0; gq < GMAX; gq++) o[gq] = 0.0f;
-#pragma unroll 4
-        for (int j = j0; j <= j1; j++) {
-            const float vv = ib::to_f32(v_cache[rowoff[j] * dv + c]);
+        for (int gq = 0; gq < GMAX; gq++) o0[gq] = o1[gq] = 0.0f;
+        for (int js = j0; js <= j1; js += VT) {
+            const int nj = min(VT, j1 - js + 1);
+            const int per_row = dv / PER;
+            __syncthreads();                                 // the last sub-tile has been read
+            for (int i = tid; i < nj * per_row; i += KC) {
+                const int jj = i / per_row, e = (i - jj * per_row) * PER;
+                *reinterpret_cast<uint4*>(vt + jj * dv + e) = *reinterpret_cast<const uint4*>(v_cache + rowoff[js + jj] * dv + e);
+            }
+            __syncthreads();
+            for (int jj = 0; jj < nj; jj++) {
+                const float va = tid < dv ? ib::to_f32(vt[jj * dv + tid]) : 0.0f;
+                const float vb = (n_c > 1 && tid + KC < dv) ? ib::to_f32(vt[jj * dv + tid + KC]) : 0.0f;
 #pragma unroll
-            for (int gq = 0; gq < GMAX; gq++)
-                if (gq < group) o[gq] = fmaf(sc[gq * KC + j], vv, o[gq]);
+                for (int gq = 0; gq < GMAX; gq++) {
+                    if (gq < group) {
+                        const float pj = sc[gq * KC + js + jj];
+                        o0[gq] = fmaf(pj, va, o0[gq]);
+                        o1[gq] = fmaf(pj, vb, o1[gq]);
+                    }
+                }
+            }
         }
 #pragma unroll
-        for (int gq = 0; gq < GMAX; gq++)
-            if (gq < group) parts[((t * n_heads + h0 + gq) * n_chunks + ci) * int64_t(dv + 2) + 2 + c] = o[gq];
+        for (int gq = 0; gq < GMAX; gq++) {
+            if (gq < group) {
+                float* dst = parts + ((t * n_heads + h0 + gq) * n_chunks + ci) * int64_t(dv + 2) + 2;
+                if (tid < dv) dst[tid] = o0[gq];
+                if (tid + KC < dv) dst[tid + KC] = o1[gq];
+            }
+        }
+    } else {
+        for (int c = tid; c < dv; c += KC) {
+            float o[GMAX];
+#pragma unroll
+            for (int gq = 0; gq < GMAX; gq++) o[gq] = 0.0f;
+#pragma unroll 4
+            for (int j = j0; j <= j1; j++) {
+                const float vv = ib::to_f32(v_cache[rowoff[j] * dv + c]);
+#pragma unroll
+                for (int gq = 0; gq < GMAX; gq++)
+                    if (gq < group) o[gq] = fmaf(sc[gq * KC + j], vv, o[gq]);
+            }
+#pragma unroll
+            for (int gq = 0; gq < GMAX; gq++)
+                if (gq < group) parts[((t * n_heads + h0 + gq) * n_chunks + ci) * int64_t(dv + 2) + 2 + c] = o[gq];
+        }
     }
     if (tid < group) {
         float* dst = parts + ((t * n_heads + h0 + tid) * n_chunks + ci) * int64_t(dv + 2);
@@ -969,7 +1021,11 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
     const int n_chunks = (visible + KC - 1) / KC + 1;
     if (n_kv > 65535 || n_chunks > 65535) return ib::fail(IB_ERR_ARG, "ib_attention_split: too many kv heads or chunks");
     const int group = n_heads / n_kv;
-    const size_t smem = size_t(group * ((d + 3) & ~3) + group * KC + 2 * GMAX) * sizeof(float) + KC * sizeof(int64_t);
+    const size_t item = dtype == IB_F32 ? 4 : 2;
+    size_t smem = size_t(group * ((d + 3) & ~3) + group * KC + 2 * GMAX) * sizeof(float) + KC * sizeof(int64_t);
+    // values through shared memory where a row is whole 16-byte pieces and at most two channels fall to a thread
+    const int vec_v = (dv * item) % 16 == 0 && dv <= 2 * KC && !(uintptr_t(v_cache) & 15) && smem + size_t(VT) * dv * item <= 48 * 1024;
+    if (vec_v) smem += size_t(VT) * dv * item;
     if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_attention_split: %d heads of %d do not fit", group, d);
     const dim3 grid{unsigned(n_tokens), unsigned(n_kv), unsigned(n_chunks)};
     const int64_t rows = n_tokens * n_heads;
@@ -977,14 +1033,14 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
         const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
         IB_LAUNCH(split_attention_kernel<float>, grid, KC, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table,
                   max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,
-                  dist_bias, bias_len, n_chunks, vec, status);
+                  dist_bias, bias_len, n_chunks, vec, vec_v, status);
         IB_LAUNCH(split_attention_merge_kernel<float>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
                   (float*)out, rows, n_heads, dv, window, n_chunks);
     } else if (dtype == IB_BF16) {
         const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
         IB_LAUNCH(split_attention_kernel<bf16>, grid, KC, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
                   max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,
-                  dist_bias, bias_len, n_chunks, vec, status);
+                  dist_bias, bias_len, n_chunks, vec, vec_v, status);
         IB_LAUNCH(split_attention_merge_kernel<bf16>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
                   (bf16*)out, rows, n_heads, dv, window, n_chunks);
     } else {

@@ -150,7 +150,10 @@ class SublayerNormBlock(Block):
         rt = self.mixer.rt
         x = h if rt.dtype == torch.float32 else self._copy_of(h, step, rt.dtype)
         fused = getattr(self.mixer, "forward_normed", None)
-        got = fused(x, step, cache, write_cache, h, self.mixer_out_norm, rt.dtype) if fused is not None else None
+        # In a decode step every kernel is a few microseconds of latency: two mixers side by side run on two streams
+        # (two branches in a captured graph) and the chains of five or six kernels take the time of the longer one.
+        side = _side_streams(h.device)[0] if (PARALLEL_BRANCHES and step.decode_only and fused is not None and rt.dtype != torch.float32) else None
+        got = fused(x, step, cache, write_cache, h, self.mixer_out_norm, rt.dtype, side) if fused is not None else None
         if got is None:
             y = self.mixer.forward(x, step, cache, None, write_cache)
             got = ops.norm_add(h, y, self.mixer_out_norm.weight, self.mixer_out_norm.eps, rt.dtype)

@@ -87,13 +87,23 @@ class SideBySide(Mixer):
             b = self.sides["second"].forward(arg(self.sides["second"]), step, cache["second"], None, write_cache)
         return a, b, self.scales["first"], self.scales["second"]
 
-    def forward_normed(self, x, step, cache, write_cache, h, out_norm, copy_dtype):
+    def forward_normed(self, x, step, cache, write_cache, h, out_norm, copy_dtype, side_stream=None):
         """For a block that normalises what the mixer returns and adds it to h: with norms on the two sides, the two
-        norms, the weighing, the block's norm and the sum are one kernel. Returns (h, its copy in copy_dtype) or None."""
+        norms, the weighing, the block's norm and the sum are one kernel. Returns (h, its copy in copy_dtype) or None.
+        With ``side_stream`` the second mixer runs there, beside the first (forked and joined by events here)."""
         if not self.normed:
             return None
         from .. import ops
-        a, b, sa, sb = self.forward_sides(x, step, cache, write_cache)
+        if side_stream is not None:
+            main = torch.cuda.current_stream(h.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side_stream.wait_event(fork)
+        a, b, sa, sb = self.forward_sides(x, step, cache, write_cache, side_stream)
+        if side_stream is not None:
+            done = torch.cuda.Event()
+            done.record(side_stream)
+            main.wait_event(done)
         return ops.dual_norm_sum(a, self.norm_w["first"], sa, b, self.norm_w["second"], sb, self.norm_eps, h, out_norm.weight,
                                  out_norm.eps, copy_dtype)
 
