@@ -107,7 +107,9 @@ class Attention(Mixer):
             raise ValueError(f"half-split rotation needs an even head_dim, got {self.head_dim}")
         self.prepared = (self.taps > 0 or self.value_norm_eps is not None or self.v_dim != self.head_dim or self.head_gate
                          or getattr(self.position, "layout", "half") == "pairs")
-        if self.prepared:
+        # (row norms, distance bias and sink have a path of their own, decided below: its kernels ask for no other library)
+        own_path = spec.get("qk_row_norm_eps") is not None or spec.get("distance_bias") is not None or bool(spec.get("sink", False))
+        if self.prepared and not own_path:
             if max(self.head_dim, self.v_dim) > ops.qkv_prepare_max_head_dim():
                 raise ValueError(f"the prepare kernel takes head sizes up to {ops.qkv_prepare_max_head_dim()}, "
                                  f"got {self.head_dim} / {self.v_dim}")
