@@ -534,7 +534,9 @@ __global__ void split_attention_merge_kernel(const float* __restrict__ parts, co
 
 // ------------------------------------------------------------------------------------------------
 // Decays of a linear attention whose key channels forget at learned, input-dependent rates:
-//   z[t, c] = bias[c] + sum_r up[c, r] * low[t, r]      (low: the rows' columns [low_col, low_col + rank), float)
+//   z[t, c] = bias[c] + sum_r up[r, c] * low[t, r]      (low: the rows' columns [low_col, low_col + rank), float;
+//                                                        up stored [rank, channels]: neighbouring threads, which
+//                                                        are neighbouring channels, read neighbouring floats)
 //   decay[t, c] = sigmoid(z) ^ (1 / tau) = exp(log_sigmoid(z) / tau)
 // and, in the same pass, q[t, c] *= q_scale in place (columns [q_col, q_col + channels) of the rows).
 __global__ void decay_gates_kernel(float* __restrict__ rows, int64_t ld, int q_col, int low_col, int rank,
@@ -546,9 +548,8 @@ __global__ void decay_gates_kernel(float* __restrict__ rows, int64_t ld, int q_c
     const int64_t t = i / channels;
     const int c = int(i - t * channels);
     const float* low = rows + t * ld + low_col;
-    const float* u = up + int64_t(c) * rank;
     float z = 0.0f;
-    for (int r = 0; r < rank; r++) z = fmaf(u[r], low[r], z);
+    for (int r = 0; r < rank; r++) z = fmaf(up[int64_t(r) * channels + c], low[r], z);
     z += bias ? bias[c] : 0.0f;
     decay[i] = expf(log_sigmoid_(z) * inv_tau);
     rows[t * ld + q_col + c] *= q_scale;

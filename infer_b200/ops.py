@@ -652,13 +652,14 @@ def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head
 
 def decay_gates(rows: torch.Tensor, q_col: int, low_col: int, rank: int, up: torch.Tensor, bias: Optional[torch.Tensor],
                 tau: float, q_scale: float) -> torch.Tensor:
-    """decay[t, c] = sigmoid(bias[c] + up[c, :] . rows[t, low_col : low_col + rank]) ^ (1 / tau), float32 [T, C] with
-    C = up.shape[0]; also multiplies columns [q_col, q_col + C) of the float32 rows by q_scale, in place."""
+    """decay[t, c] = sigmoid(bias[c] + up[:, c] . rows[t, low_col : low_col + rank]) ^ (1 / tau), float32 [T, C] with
+    ``up`` float32 [rank, C] (the low rank's second factor, transposed); also multiplies columns [q_col, q_col + C) of
+    the float32 rows by q_scale, in place."""
     _check(rows, "rows", torch.float32)
     T, ld = rows.shape
     _check(up, "up", torch.float32)
-    C = up.shape[0]
-    if up.shape[1] != rank or low_col + rank > ld or q_col + C > ld:
+    C = up.shape[1]
+    if up.shape[0] != rank or low_col + rank > ld or q_col + C > ld:
         raise KernelError("decay_gates: the low-rank columns or q lie outside the rows")
     if bias is not None:
         _check(bias, "bias", torch.float32, (C,))

@@ -84,7 +84,7 @@ class DecayedLinearAttention(Mixer):
         self.low_col, self.gate_col = 2 * nq + nv, 2 * nq + nv + self.rank
         f32 = dict(device=self.rt.device, dtype=torch.float32)
         # the second factor keeps the values the checkpoint has, widened: its product runs in float32
-        self.up = up.to(self.rt.dtype).to(**f32).contiguous()
+        self.up = up.to(self.rt.dtype).to(**f32).t().contiguous()              # [rank, channels]
         self.up_bias = params[n["decay_bias"]].to(**f32).contiguous()
         self.norm_w = params[n["norm"]].to(**f32).contiguous()
         self.o = Linear(self.rt, params[n["o"]])

@@ -288,7 +288,7 @@ def test_decays_through_a_low_rank(sizes):
     z = rows[:, 3 + C:].double() @ up.double().T + bias.double()
     want = torch.sigmoid(z) ** (1.0 / tau)
     dev = rows.to(DEV)
-    decay = ops.decay_gates(dev, 3, 3 + C, r, up.to(DEV), bias.to(DEV), tau, d ** -0.5)
+    decay = ops.decay_gates(dev, 3, 3 + C, r, up.t().contiguous().to(DEV), bias.to(DEV), tau, d ** -0.5)
     assert torch.allclose(decay.double().cpu(), want, rtol=1e-5, atol=1e-6)
     assert torch.allclose(dev[:, 3:3 + C].double().cpu(), rows[:, 3:3 + C].double() * d ** -0.5, rtol=1e-6, atol=1e-7)
     assert torch.equal(dev[:, :3].cpu(), rows[:, :3]) and torch.equal(dev[:, 3 + C:].cpu(), rows[:, 3 + C:])
