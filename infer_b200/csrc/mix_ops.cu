@@ -328,7 +328,8 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&x)[8]) {
     }
 }
 
-template <typename T>
+// GB: the group's size rounded up to 1, 2, 4, 8 or 16 (the loops over a group's heads are unrolled to it).
+template <typename T, int GB>
 __global__ void __launch_bounds__(KC)
 split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
@@ -359,9 +360,9 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     const int* table = block_table + int64_t(sg) * max_blocks;
     const int key = base + tid;
     const bool valid = key >= lo && key <= pos;
-    float acc[GMAX];
+    float acc[GB];
 #pragma unroll
-    for (int gq = 0; gq < GMAX; gq++) acc[gq] = 0.0f;
+    for (int gq = 0; gq < GB; gq++) acc[gq] = 0.0f;
     bool have = false;
     if (valid) {
         const int page = table[key / page_size];
@@ -386,7 +387,7 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                         const int e = e0 + 8 * b4;
                         if (e < d) {
 #pragma unroll
-                            for (int gq = 0; gq < GMAX; gq++) {
+                            for (int gq = 0; gq < GB; gq++) {
                                 if (gq < group) {
                                     const float4 a = *reinterpret_cast<const float4*>(qs + gq * dq + e);
                                     const float4 b = *reinterpret_cast<const float4*>(qs + gq * dq + e + 4);
@@ -403,7 +404,7 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                 for (int e = 0; e < d; e++) {
                     const float kv = ib::to_f32(kr[e]);
 #pragma unroll
-                    for (int gq = 0; gq < GMAX; gq++)
+                    for (int gq = 0; gq < GB; gq++)
                         if (gq < group) acc[gq] = fmaf(qs[gq * dq + e], kv, acc[gq]);
                 }
             }
@@ -412,7 +413,7 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         rowoff[tid] = 0;
     }
 #pragma unroll
-    for (int gq = 0; gq < GMAX; gq++) {
+    for (int gq = 0; gq < GB; gq++) {
         if (gq < group) {
             float sv = -INFINITY;
             if (have) {
@@ -445,9 +446,9 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         T* vt = reinterpret_cast<T*>(rowoff + KC);           // [VT][dv]
         constexpr int PER = 16 / int(sizeof(T));             // values per 16-byte load
         const int n_c = (dv + KC - 1) / KC;                  // channel passes of a thread (dv <= 2 KC)
-        float o0[GMAX], o1[GMAX];
+        float o0[GB], o1[GB];
 #pragma unroll
-        for (int gq = 0; gq < GMAX; gq++) o0[gq] = o1[gq] = 0.0f;
+        for (int gq = 0; gq < GB; gq++) o0[gq] = o1[gq] = 0.0f;
         for (int js = j0; js <= j1; js += VT) {
             const int nj = min(VT, j1 - js + 1);
             const int per_row = dv / PER;
@@ -457,21 +458,31 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                 *reinterpret_cast<uint4*>(vt + jj * dv + e) = *reinterpret_cast<const uint4*>(v_cache + rowoff[js + jj] * dv + e);
             }
             __syncthreads();
-            for (int jj = 0; jj < nj; jj++) {
-                const float va = tid < dv ? ib::to_f32(vt[jj * dv + tid]) : 0.0f;
-                const float vb = (n_c > 1 && tid + KC < dv) ? ib::to_f32(vt[jj * dv + tid + KC]) : 0.0f;
+            if (n_c > 1) {
+                for (int jj = 0; jj < nj; jj++) {
+                    const float va = tid < dv ? ib::to_f32(vt[jj * dv + tid]) : 0.0f;
+                    const float vb = tid + KC < dv ? ib::to_f32(vt[jj * dv + tid + KC]) : 0.0f;
 #pragma unroll
-                for (int gq = 0; gq < GMAX; gq++) {
-                    if (gq < group) {
-                        const float pj = sc[gq * KC + js + jj];
-                        o0[gq] = fmaf(pj, va, o0[gq]);
-                        o1[gq] = fmaf(pj, vb, o1[gq]);
+                    for (int gq = 0; gq < GB; gq++) {
+                        if (gq < group) {
+                            const float pj = sc[gq * KC + js + jj];
+                            o0[gq] = fmaf(pj, va, o0[gq]);
+                            o1[gq] = fmaf(pj, vb, o1[gq]);
+                        }
                     }
+                }
+            } else {
+#pragma unroll 4
+                for (int jj = 0; jj < nj; jj++) {
+                    const float va = tid < dv ? ib::to_f32(vt[jj * dv + tid]) : 0.0f;
+#pragma unroll
+                    for (int gq = 0; gq < GB; gq++)
+                        if (gq < group) o0[gq] = fmaf(sc[gq * KC + js + jj], va, o0[gq]);
                 }
             }
         }
 #pragma unroll
-        for (int gq = 0; gq < GMAX; gq++) {
+        for (int gq = 0; gq < GB; gq++) {
             if (gq < group) {
                 float* dst = parts + ((t * n_heads + h0 + gq) * n_chunks + ci) * int64_t(dv + 2) + 2;
                 if (tid < dv) dst[tid] = o0[gq];
@@ -480,18 +491,18 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         }
     } else {
         for (int c = tid; c < dv; c += KC) {
-            float o[GMAX];
+            float o[GB];
 #pragma unroll
-            for (int gq = 0; gq < GMAX; gq++) o[gq] = 0.0f;
+            for (int gq = 0; gq < GB; gq++) o[gq] = 0.0f;
 #pragma unroll 4
             for (int j = j0; j <= j1; j++) {
                 const float vv = ib::to_f32(v_cache[rowoff[j] * dv + c]);
 #pragma unroll
-                for (int gq = 0; gq < GMAX; gq++)
+                for (int gq = 0; gq < GB; gq++)
                     if (gq < group) o[gq] = fmaf(sc[gq * KC + j], vv, o[gq]);
             }
 #pragma unroll
-            for (int gq = 0; gq < GMAX; gq++)
+            for (int gq = 0; gq < GB; gq++)
                 if (gq < group) parts[((t * n_heads + h0 + gq) * n_chunks + ci) * int64_t(dv + 2) + 2 + c] = o[gq];
         }
     }
@@ -1030,23 +1041,30 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
     if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_attention_split: %d heads of %d do not fit", group, d);
     const dim3 grid{unsigned(n_tokens), unsigned(n_kv), unsigned(n_chunks)};
     const int64_t rows = n_tokens * n_heads;
+    const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
+    const int gb = group <= 1 ? 1 : (group <= 2 ? 2 : (group <= 4 ? 4 : (group <= 8 ? 8 : 16)));
+#define IB_SPLIT(TT, GG)                                                                                                          \
+    IB_LAUNCH((split_attention_kernel<TT, GG>), grid, KC, smem, (const TT*)q, (const TT*)k_cache, (const TT*)v_cache, block_table, \
+              max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,  \
+              dist_bias, bias_len, n_chunks, vec, vec_v, status)
+#define IB_SPLIT_BY_GROUP(TT)                                                                                                     \
+    do {                                                                                                                          \
+        if (gb == 1) IB_SPLIT(TT, 1); else if (gb == 2) IB_SPLIT(TT, 2); else if (gb == 4) IB_SPLIT(TT, 4);                       \
+        else if (gb == 8) IB_SPLIT(TT, 8); else IB_SPLIT(TT, 16);                                                                 \
+    } while (0)
     if (dtype == IB_F32) {
-        const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
-        IB_LAUNCH(split_attention_kernel<float>, grid, KC, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table,
-                  max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,
-                  dist_bias, bias_len, n_chunks, vec, vec_v, status);
+        IB_SPLIT_BY_GROUP(float);
         IB_LAUNCH(split_attention_merge_kernel<float>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
                   (float*)out, rows, n_heads, dv, window, n_chunks);
     } else if (dtype == IB_BF16) {
-        const int vec = d % 8 == 0 && !(uintptr_t(k_cache) & 15);
-        IB_LAUNCH(split_attention_kernel<bf16>, grid, KC, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                  max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,
-                  dist_bias, bias_len, n_chunks, vec, vec_v, status);
+        IB_SPLIT_BY_GROUP(bf16);
         IB_LAUNCH(split_attention_merge_kernel<bf16>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
                   (bf16*)out, rows, n_heads, dv, window, n_chunks);
     } else {
         return ib::fail(IB_ERR_ARG, "ib_attention_split: unknown dtype %d", dtype);
     }
+#undef IB_SPLIT_BY_GROUP
+#undef IB_SPLIT
     return ib::check_launch("ib_attention_split");
 }
 
