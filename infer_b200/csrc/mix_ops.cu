@@ -590,9 +590,16 @@ __device__ __forceinline__ float filtered(const float* __restrict__ rows, int64_
 // One warp per (token, unit): G units of a (q, k) head pair, H units of a v head, one unit for the heads' scalars.
 constexpr int PREP_PER_LANE = 8;         // heads of up to 32 * PREP_PER_LANE channels
 
+// The newest input of channel c joins its request's tail, the oldest leaves (steps of one token per request: the lane
+// that filtered the channel is the tail's only reader).
+__device__ __forceinline__ void shift_tail(float* tail, int64_t channels, int taps, int c, float newest) {
+    for (int idx = 0; idx + 1 < taps - 1; idx++) tail[int64_t(idx) * channels + c] = tail[int64_t(idx + 1) * channels + c];
+    tail[int64_t(taps - 2) * channels + c] = newest;
+}
+
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ rows, int64_t ld, int col0, int a_col, int b_col,
-                     const float* __restrict__ filt_w, int taps, const float* __restrict__ tails,
+                     const float* __restrict__ filt_w, int taps, float* tails, int inline_tail,
                      const float* __restrict__ a_log, const float* __restrict__ dt_bias, float unit_eps, float q_scale,
                      const int* __restrict__ token_seg, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                      float* __restrict__ prep, int64_t ldp, int64_t n_tokens, int n_heads, int n_qk, int d, int dv) {
@@ -606,7 +613,8 @@ delta_prepare_kernel(const float* __restrict__ rows, int64_t ld, int col0, int a
     const int channels = 2 * n_qk * d + n_heads * dv;
     const int s = token_seg[t];
     const int i_local = int(t - seg_start[s]);
-    const float* tail = taps > 1 ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels : nullptr;
+    float* tail = taps > 1 ? tails + (int64_t(seg_slot[s]) * (taps - 1)) * channels : nullptr;
+    const bool move = inline_tail && taps > 1;
     float* out = prep + t * ldp;
     const int g_off = 2 * n_qk * d + n_heads * dv;
     if (u < n_qk) {
@@ -620,6 +628,10 @@ delta_prepare_kernel(const float* __restrict__ rows, int64_t ld, int col0, int a
                 const int cq = u * d + j, ck = n_qk * d + u * d + j;
                 qv[r] = silu_(filtered(rows, ld, t, i_local, col0 + cq, filt_w + cq, channels, taps, tail + cq, channels));
                 kv[r] = silu_(filtered(rows, ld, t, i_local, col0 + ck, filt_w + ck, channels, taps, tail + ck, channels));
+                if (move) {
+                    shift_tail(tail, channels, taps, cq, rows[t * ld + col0 + cq]);
+                    shift_tail(tail, channels, taps, ck, rows[t * ld + col0 + ck]);
+                }
                 sq = fmaf(qv[r], qv[r], sq);
                 sk = fmaf(kv[r], kv[r], sk);
                 dot = fmaf(qv[r], kv[r], dot);
@@ -643,6 +655,7 @@ delta_prepare_kernel(const float* __restrict__ rows, int64_t ld, int col0, int a
         for (int j = lane; j < dv; j += 32) {
             const int c = 2 * n_qk * d + h * dv + j;
             out[c] = silu_(filtered(rows, ld, t, i_local, col0 + c, filt_w + c, channels, taps, tail + c, channels));
+            if (move) shift_tail(tail, channels, taps, c, rows[t * ld + col0 + c]);
         }
     } else {
         for (int h = lane; h < n_heads; h += 32) {
@@ -1080,8 +1093,9 @@ IB_EXPORT int ib_decay_gates(float* rows, int64_t ld, int q_col, int low_col, in
 // The widest (q, k) head that ib_delta_prepare takes.
 IB_EXPORT int ib_delta_prepare_max_dim() { return 32 * PREP_PER_LANE; }
 
+// inline_tail (only for steps of one token per request): the kernel also moves the tails.
 IB_EXPORT int ib_delta_prepare(const float* rows, int64_t ld, int col0, int a_col, int b_col, const float* filt_w, int taps,
-                               const float* tails, const float* a_log, const float* dt_bias, float unit_eps, float q_scale,
+                               float* tails, int inline_tail, const float* a_log, const float* dt_bias, float unit_eps, float q_scale,
                                const int* token_seg, const int* seg_start, const int* seg_slot, float* prep, int64_t ldp,
                                int64_t n_tokens, int n_heads, int n_qk, int d, int dv, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
@@ -1090,7 +1104,8 @@ IB_EXPORT int ib_delta_prepare(const float* rows, int64_t ld, int col0, int a_co
     if (filt_w && taps > 1 && !tails) return ib::fail(IB_ERR_ARG, "ib_delta_prepare: a filter of %d taps needs tails", taps);
     if (ldp < 2 * int64_t(n_qk) * d + int64_t(n_heads) * dv + 2 * n_heads + n_qk) return ib::fail(IB_ERR_ARG, "ib_delta_prepare: prepared rows too short");
     const int64_t warps = n_tokens * (n_qk + n_heads + 1);
-    IB_LAUNCH(delta_prepare_kernel, blocks_for(warps, 4), 128, 0, rows, ld, col0, a_col, b_col, filt_w, filt_w ? taps : 0, tails, a_log,
+    IB_LAUNCH(delta_prepare_kernel, blocks_for(warps, 4), 128, 0, rows, ld, col0, a_col, b_col, filt_w, filt_w ? taps : 0, tails,
+              (filt_w && taps > 1) ? inline_tail : 0, a_log,
               dt_bias, unit_eps, q_scale, token_seg, seg_start, seg_slot, prep, ldp, n_tokens, n_heads, n_qk, d, dv);
     return ib::check_launch("ib_delta_prepare");
 }

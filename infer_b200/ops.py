@@ -681,11 +681,12 @@ def state_scan_max_dim() -> int:
 
 def delta_prepare(rows: torch.Tensor, col0: int, a_col: int, b_col: int, filt_w: Optional[torch.Tensor],
                   tails: Optional[torch.Tensor], a_log: torch.Tensor, dt_bias: torch.Tensor, unit_eps: float, q_scale: float,
-                  step, n_heads: int, n_qk: int, dim: int, v_dim: int) -> torch.Tensor:
+                  step, n_heads: int, n_qk: int, dim: int, v_dim: int, inline_tail: bool = False) -> torch.Tensor:
     """What the gated delta rule reads, from float32 projected rows [.. q (n_qk x dim) | k | v (n_heads x v_dim) ..]
     (from column col0; per-head step-size logits at a_col, write-strength logits at b_col): every q, k, v channel
     through its causal filter (``filt_w`` float32 [taps, channels], ``tails`` float32 [slots, taps - 1, channels]) and
-    silu; q and k made unit vectors per head, q times q_scale. Returns float32 [T, q | k | v | g | beta | k.q]."""
+    silu; q and k made unit vectors per head, q times q_scale. Returns float32 [T, q | k | v | g | beta | k.q].
+    ``inline_tail`` (only for steps of one token per request): the kernel also moves the tails (no ``tail_update``)."""
     _check(rows, "rows", torch.float32)
     T, ld = rows.shape
     C = 2 * n_qk * dim + n_heads * v_dim
@@ -705,10 +706,10 @@ def delta_prepare(rows: torch.Tensor, col0: int, a_col: int, b_col: int, filt_w:
     _check(dt_bias, "dt_bias", torch.float32, (n_heads,))
     ldp = (C + 2 * n_heads + n_qk + 3) // 4 * 4
     prep = torch.empty((T, ldp), dtype=torch.float32, device=rows.device)
-    f = _fn("mix", "ib_delta_prepare", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
+    f = _fn("mix", "ib_delta_prepare", [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float,
                                         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p])
     _call(f, rows.data_ptr(), ld, int(col0), int(a_col), int(b_col), _ptr(filt_w), taps, _ptr(tails) if taps > 1 else None,
-          a_log.data_ptr(), dt_bias.data_ptr(), float(unit_eps), float(q_scale), step.token_seg.data_ptr(), step.seg_start.data_ptr(),
+          int(bool(inline_tail)), a_log.data_ptr(), dt_bias.data_ptr(), float(unit_eps), float(q_scale), step.token_seg.data_ptr(), step.seg_start.data_ptr(),
           step.seg_slot.data_ptr(), prep.data_ptr(), ldp, T, n_heads, n_qk, dim, v_dim, _stream())
     return prep
 

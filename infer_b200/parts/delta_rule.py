@@ -113,9 +113,11 @@ class GatedDeltaRule(Mixer):
     def forward(self, x, step, cache, residual, write_cache=True):
         rows = self.proj(x, out_dtype=torch.float32)
         tails = cache.get("tails")
+        # with one token per request, the lane that filters a channel is the only reader of its tail and moves it too
+        inline_tail = tails is not None and write_cache and step.max_q_len == 1
         prep = ops.delta_prepare(rows, 0, self.step_col, self.beta_col, self.filter_w, tails, self.a_log, self.dt_bias,
-                                 self.unit_eps, float(self.dim) ** -0.5, step, self.n_heads, self.n_qk, self.dim, self.v_dim)
-        if tails is not None and write_cache:
+                                 self.unit_eps, float(self.dim) ** -0.5, step, self.n_heads, self.n_qk, self.dim, self.v_dim, inline_tail)
+        if tails is not None and write_cache and not inline_tail:
             ops.tail_update(rows, 0, tails, step.seg_start, step.seg_slot)
         nqk = self.n_qk * self.dim
         o = ops.state_scan(ops.SCAN_DELTA_RULE, prep, 0, nqk, 2 * nqk, prep, self.channels, cache["S"], step.seg_start,

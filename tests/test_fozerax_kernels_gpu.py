@@ -371,9 +371,10 @@ def test_delta_rule_from_projected_rows(sizes, taps):
         step = _Step(lens, [at[0], at[2]], [0, 2])
         T = sum(lens)
         rows = torch.cat([torch.full((T, 3), 7.0), torch.cat([seqs[0][at[0]:at[0] + lens[0]], seqs[2][at[2]:at[2] + lens[1]]])], dim=1).contiguous().to(DEV)
+        inline = tails is not None and max(lens) == 1           # steps of single tokens: the kernel moves the tails itself
         prep = ops.delta_prepare(rows, 3, 3 + C, 3 + C + H, fw.t().contiguous().to(DEV) if taps else None, tails, a_log.to(DEV), dt_bias.to(DEV),
-                                 pf.UNIT_EPS, d ** -0.5, step, H, G, d, dv)
-        if tails is not None:
+                                 pf.UNIT_EPS, d ** -0.5, step, H, G, d, dv, inline)
+        if tails is not None and not inline:
             ops.tail_update(rows, 3, tails, step.seg_start, step.seg_slot)
         o = ops.state_scan(ops.SCAN_DELTA_RULE, prep, 0, G * d, 2 * G * d, prep, C, state, step.seg_start, step.seg_slot, H, H // G, d, dv,
                            True, max(lens)).double().cpu().view(T, H, dv)
