@@ -53,12 +53,12 @@ CASES: Dict[str, dict] = {
                       "mlp": {"kind": "dense", "ff": 20}},
                      {"type": "parallel", "mixer": _par(_left(1, 1, 6, 14, 0.5, 30, 33, 16), _right(1, 1, 12, 6, 0)),
                       "mlp": _moe(9, 3, (3, 1), 5, 3.0, (7, 0.5))}]},
-    # large heads: keys of 128 and 96 (sixteen and thirty-two state rows a lane), a window of 72 under a table that
+    # large heads: keys of 128 and 160 (sixteen and thirty-two state rows a lane), a window of 80 under a table that
     # saturates later, two decayed layers in a row
     "c": {"architecture": "Fozerax", "vocab": 256, "width": 128, "norm": {"eps": 2e-6},
           "layers": [{"type": "gla", "mixer": _gla(2, 128, 64, 16.0, 16), "mlp": _moe(8, 2, (4, 2), 32, 2.0, (64, 1.0))},
                      {"type": "gla", "mixer": _gla(3, 24, 40, 4.0, 8), "mlp": None},
-                     {"type": "parallel", "mixer": _par(_left(8, 2, 64, 64, 0.125, 200, 72, 32), _right(4, 2, 160, 128, 4)),
+                     {"type": "parallel", "mixer": _par(_left(8, 2, 64, 64, 0.11, 200, 80, 28), _right(4, 2, 160, 128, 4)),
                       "mlp": {"kind": "dense", "ff": 256}}]},
 }
 

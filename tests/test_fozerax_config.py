@@ -132,20 +132,20 @@ def test_cache_needs_windows_and_slots_used_again():
 
 
 def test_bucket_function_and_bias_table():
-    B, D = 32, 120.0
+    B, D = 24, 90.0
     rows = [log_bucket(n, B, D) for n in range(200)]
-    assert rows[:16] == list(range(16)) and rows[16] == 16 and max(rows) == B - 1 and rows == sorted(rows)
+    assert rows[:12] == list(range(12)) and rows[12] == 12 and max(rows) == B - 1 and rows == sorted(rows)
     assert all(log_bucket(n, B, D) == pf.distance_bucket(n, B, D) for n in range(300))
-    assert rows[119] < B - 1 or rows[120] == B - 1
+    assert rows[89] < B - 1 or rows[90] == B - 1
     assert log_bucket(int(D), B, D) == B - 1
     assert [log_bucket(n, 7, 20.0) for n in range(4)] == [0, 1, 2, 3]                      # an odd table: B // 2 single rows
     rel = torch.arange(B * 2, dtype=torch.float32).view(B, 2)
-    t = distance_bias_table(rel, D, 72)
-    assert t.shape == (72, 2) and torch.equal(t[5], rel[5]) and torch.equal(t[71], rel[log_bucket(71, B, D)])
+    t = distance_bias_table(rel, D, 50)
+    assert t.shape == (50, 2) and torch.equal(t[5], rel[5]) and torch.equal(t[49], rel[log_bucket(49, B, D)])
     t = distance_bias_table(rel, D, None)
     assert torch.equal(t[-1], rel[B - 1]) and log_bucket(t.shape[0] - 2, B, D) < B - 1       # the last row stands for all beyond
     with pytest.raises(ValueError):
-        distance_bias_table(rel, 16.0, None)
+        distance_bias_table(rel, 12.0, None)
 
 
 def test_plain_scans_can_be_cut_anywhere():

@@ -43,7 +43,7 @@ def test_whole(name, dtype):
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 @pytest.mark.parametrize("name", ["a", "b", "c"])
 def test_tail_one_by_one(name, dtype):
-    """The last 40 tokens decoded one by one: windows of 5, 24, 33 and 72 pass over decoded tokens."""
+    """The last 40 tokens decoded one by one: windows of 5, 24, 33 and 80 pass over decoded tokens."""
     reqs = _requests(name, [110, 47], seed0=10)
     got = H.run_trace(_engine(name, dtype), H.trace_tail(reqs, 40))
     FC.check(FC.CASES[name], SEED, dtype, got, reqs, what=name)

@@ -125,7 +125,7 @@ def test_row_norms_of_q_and_k_and_the_cache_write(dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("window", [None, 5, 16, 33, 72])
+@pytest.mark.parametrize("window", [None, 5, 16, 33, 70])
 def test_attention_with_distance_bias_window_and_sink(dtype, window):
     """Keys at the window's two edges carry the result: the key at distance window - 1 is made to stand out for one
     head, the key at distance window (just outside) for another, by scaling those keys along the query."""
@@ -196,7 +196,7 @@ def test_tensor_core_attention_with_distance_bias_and_sink(sizes, window):
     stand out for two heads of the portion's last rows."""
     from infer_b200.parts.attention import distance_bias_table
     H, G, d = sizes
-    B, D, scale, dtype = 32, 120.0, 0.11, torch.bfloat16
+    B, D, scale, dtype = 28, 150.0, 0.11, torch.bfloat16
     g = torch.Generator().manual_seed(d + (window or 0))
     n, m = 500, 90                                              # the portion's request; the single token's request
     seqs = []
@@ -235,7 +235,7 @@ def test_tensor_core_attention_with_distance_bias_and_sink(sizes, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("window", [None, 5, 72, 128, 300])
+@pytest.mark.parametrize("window", [None, 5, 70, 128, 300])
 @pytest.mark.parametrize("sizes", [(6, 2, 64, 48), (3, 3, 10, 7), (16, 1, 128, 128), (4, 2, 24, 40)])
 def test_single_tokens_with_their_keys_split_over_ctas(sizes, window, dtype):
     """Decoded tokens at positions around chunk borders (multiples of 128), page borders and the first positions; one
